@@ -1,2 +1,3 @@
 """Architectures this engine knows; importing the package registers them."""
 from . import llama  # noqa: F401
+from . import turudra  # noqa: F401

@@ -63,8 +63,16 @@ def load_config(model_dir: str):
     Returns (architecture entry, typed configuration).
     """
     d = read_config_json(model_dir)
-    archs = d.get("architectures")
-    if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a list holding one name")
-    arch = resolve(archs[0])
+    return_name = architecture_name(d)
+    arch = resolve(return_name)
     return arch, arch.config_from_dict(d)
+
+
+def architecture_name(d: dict) -> str:
+    """The architecture a config.json names: `architectures` (a list holding one name) or `architecture` (the name)."""
+    archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        return d["architecture"]
+    if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
+        raise ConfigError("config.json: 'architectures' must be a list holding one name (or 'architecture' the name)")
+    return archs[0]

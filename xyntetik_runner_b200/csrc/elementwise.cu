@@ -12,7 +12,7 @@
 // on the device (the one it sampled), so that the host need not have seen it when it describes this step.
 template <typename TW>
 __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ feed,
-                        float* __restrict__ x, int d, int vocab, int n_feed) {
+                        float* __restrict__ x, int d, int vocab, int n_feed, float scale) {
     xr_pdl_launch();
     // The token ids are part of the step's description and the table is a weight: the row is read before the kernel
     // ahead is complete, sixteen values a thread in one run of loads; only the stores wait.  (A fed token is another
@@ -38,16 +38,17 @@ __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ id
 #pragma unroll
         for (int k = 0; k < 16; k++) {
             int i = i0 + k * blockDim.x;
-            if (i < d) out[i] = xr_to_f32<TW>(v[k]);
+            if (i < d) out[i] = xr_to_f32<TW>(v[k]) * scale;
         }
     }
 }
 
+// x[t] = E[id_t] * scale (scale 1 for a model without an embedding multiplier: the product is then exact)
 XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, const int* feed, int n_feed, float* x, int n, int d,
-                       int vocab, cudaStream_t stream) {
+                       int vocab, float scale, cudaStream_t stream) {
     if (n < 1 || d < 1 || vocab < 1 || n_feed < 0) return XR_ERR_ARG;
-    if (table_dtype == XR_F32) xr_launch((k_embed<float>), dim3(n), dim3(256), 0, stream, (const float*)table, ids, feed, x, d, vocab, n_feed);
-    else if (table_dtype == XR_BF16) xr_launch((k_embed<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, feed, x, d, vocab, n_feed);
+    if (table_dtype == XR_F32) xr_launch((k_embed<float>), dim3(n), dim3(256), 0, stream, (const float*)table, ids, feed, x, d, vocab, n_feed, scale);
+    else if (table_dtype == XR_BF16) xr_launch((k_embed<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, feed, x, d, vocab, n_feed, scale);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -335,27 +336,37 @@ __device__ __forceinline__ float xr_activation(int act, float g) {
     return g;
 }
 
+// act 3 (gated only): with g' = min(g, limit) and u' = u clamped to [-limit, limit], h = g' sigmoid(1.702 g') (u' + 1).
+__device__ __forceinline__ float xr_gate(int act, float limit, float g, float u) {
+    if (act == 3) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return xr_activation(act, g) * u;
+}
+
 template <typename T>
-__global__ void k_act_mul(const T* gu, T* h, int n, int F, int act, int gated) {       // (h may be gu: no __restrict__)
+__global__ void k_act_mul(const T* gu, T* h, int n, int F, int act, int gated, float limit) {       // (h may be gu: no __restrict__)
     xr_pdl_launch();
     xr_pdl_wait();
     size_t total = (size_t)n * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / F, f = i % F;
         float v;
-        if (gated) v = xr_activation(act, xr_to_f32<T>(gu[t * 2 * F + f])) * xr_to_f32<T>(gu[t * 2 * F + F + f]);
+        if (gated) v = xr_gate(act, limit, xr_to_f32<T>(gu[t * 2 * F + f]), xr_to_f32<T>(gu[t * 2 * F + F + f]));
         else v = xr_activation(act, xr_to_f32<T>(gu[i]));
         h[i] = xr_from_f32<T>(v);
     }
 }
 
 // gated: gu [n, 2F] -> h [n, F]; ungated: gu [n, F] -> h [n, F] (h may be gu)
-XR_EXPORT int xr_act_mul(const void* gu, void* h, int dtype, int n, int F, int act, int gated, cudaStream_t stream) {
-    if (n < 1 || F < 1 || act < 0 || act > 2) return XR_ERR_ARG;
+XR_EXPORT int xr_act_mul(const void* gu, void* h, int dtype, int n, int F, int act, int gated, float limit, cudaStream_t stream) {
+    if (n < 1 || F < 1 || act < 0 || act > 3 || (act == 3 && !gated)) return XR_ERR_ARG;
     size_t total = (size_t)n * F;
     int blocks = (int)((total + 255) / 256 < (size_t)xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
-    if (dtype == XR_F32) xr_launch((k_act_mul<float>), dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)h, n, F, act, gated);
-    else if (dtype == XR_BF16) xr_launch((k_act_mul<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, n, F, act, gated);
+    if (dtype == XR_F32) xr_launch((k_act_mul<float>), dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)h, n, F, act, gated, limit);
+    else if (dtype == XR_BF16) xr_launch((k_act_mul<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, n, F, act, gated, limit);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -379,6 +390,67 @@ XR_EXPORT int xr_residual_add(float* x, const void* dlt, int dtype, int n, int d
     if (dtype == XR_F32) xr_launch((k_residual_add<float>), dim3(blocks), dim3(256), 0, stream, x, (const float*)dlt, total);
     else if (dtype == XR_BF16) xr_launch((k_residual_add<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, x, (const __nv_bfloat16*)dlt, total);
     else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// x[t][i] += m * d[t][i] on float32 streams: a block that runs its sublayers side by side collects their sum in d
+// and adds it to the residual stream once, times the model's residual multiplier.
+// ---------------------------------------------------------------------------
+__global__ void k_scaled_add(float* __restrict__ x, const float* __restrict__ d, float m, size_t total) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = fmaf(m, d[i], x[i]);
+}
+
+XR_EXPORT int xr_scaled_add(float* x, const float* d, float m, int n, int width, cudaStream_t stream) {
+    if (n < 1 || width < 1) return XR_ERR_ARG;
+    size_t total = (size_t)n * width;
+    int blocks = (int)((total + 255) / 256 < (size_t)xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
+    xr_launch(k_scaled_add, dim3(blocks), dim3(256), 0, stream, x, d, m, total);
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// out[t] = [a[t] ; b[t]] of two float32 streams, in the activation dtype: the input of a product over both.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void k_concat_cast(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int n, int width) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    size_t total = (size_t)n * 2 * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t t = i / (2 * (size_t)width), c = i % (2 * (size_t)width);
+        out[i] = xr_from_f32<T>(c < (size_t)width ? a[t * width + c] : b[t * width + c - width]);
+    }
+}
+
+XR_EXPORT int xr_concat_cast(const float* a, const float* b, void* out, int dtype, int n, int width, cudaStream_t stream) {
+    if (n < 1 || width < 1) return XR_ERR_ARG;
+    size_t total = (size_t)n * 2 * width;
+    int blocks = (int)((total + 255) / 256 < (size_t)xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
+    if (dtype == XR_F32) xr_launch((k_concat_cast<float>), dim3(blocks), dim3(256), 0, stream, a, b, (float*)out, n, width);
+    else if (dtype == XR_BF16) xr_launch((k_concat_cast<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, a, b, (__nv_bfloat16*)out, n, width);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Soft cap of float32 logits in place: z <- cap * tanh(z / cap).
+// ---------------------------------------------------------------------------
+__global__ void k_softcap(float* __restrict__ z, float cap, size_t total) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const float inv = 1.0f / cap;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        z[i] = cap * tanhf(z[i] * inv);
+}
+
+XR_EXPORT int xr_softcap(float* z, float cap, long long total, cudaStream_t stream) {
+    if (total < 1 || !(cap > 0.f)) return XR_ERR_ARG;
+    int blocks = (int)((total + 255) / 256 < (long long)xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
+    xr_launch(k_softcap, dim3(blocks), dim3(256), 0, stream, z, cap, (size_t)total);
     return xr_launch_status();
 }
 

@@ -49,6 +49,7 @@ __host__ __device__ constexpr int tc_threads(int bn) { return bn <= 16 ? 192 : T
 #define TC_ACT_NONE 0
 #define TC_ACT_SILU 1
 #define TC_ACT_GELU_TANH 2
+#define TC_ACT_SWISH_CLAMP 3     // gated products only, see tc_gate
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -123,6 +124,16 @@ __device__ __forceinline__ float tc_gelu_tanh(float g) {
 __device__ __forceinline__ float tc_act(int act, float g) {
     return act == TC_ACT_SILU ? tc_silu(g) : (act == TC_ACT_GELU_TANH ? tc_gelu_tanh(g) : g);
 }
+// What a gated product stores for a feature with gate sum g and up sum u: act(g) * u, or for TC_ACT_SWISH_CLAMP
+// g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit) and u' = u clamped to [-limit, limit].
+__device__ __forceinline__ float tc_gate(int act, float limit, float g, float u) {
+    if (act == TC_ACT_SWISH_CLAMP) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return tc_act(act, g) * u;
+}
 
 // K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, groups of 8 rows 1024 bytes
 // apart: start address and offsets in 16-byte units, descriptor version 1 (bit 46), layout type 2 (bits 61-63).
@@ -150,6 +161,7 @@ struct TcParams {
     int splits;                 // z-slices of the grid; slice z handles K blocks [z*total/splits, (z+1)*total/splits)
     int epilogue, out_dtype;
     int act;                    // TC_ACT_*: applied to the stored value (store epilogue) or to the gate (gated epilogue)
+    float act_limit;            // the clamp of TC_ACT_SWISH_CLAMP
     int gated;                  // the product's rows are gate and up rows interleaved (also when the epilogue is PARTIAL)
     int bn;                     // tokens per tile: a multiple of 16, at most the kernel's BN (which sizes the buffers)
     int packed;                 // W is stored tile by tile: [row tile][K block][128][64], see xr_gemm_tc
@@ -191,7 +203,7 @@ __device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_bas
             const int col0 = tok0 + c0 + (up_lane ? 8 : 0);
             float v[8];
 #pragma unroll
-            for (int c = 0; c < 8; c++) v[c] = up_lane ? tc_act(p.act, other[c]) * g[8 + c] : tc_act(p.act, g[c]) * other[c];
+            for (int c = 0; c < 8; c++) v[c] = up_lane ? tc_gate(p.act, p.act_limit, other[c], g[8 + c]) : tc_gate(p.act, p.act_limit, g[c], other[c]);
             if (p.out_dtype == XR_BF16) {
                 __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)col0 * p.ldo + f;
 #pragma unroll
@@ -552,6 +564,7 @@ struct FinishParams {
     const float* partial; void* out; const float* bias;
     long long ldo;
     int n, n_out, splits, epilogue, out_dtype, gated, act;
+    float act_limit;
 };
 
 __global__ void k_splitk_finish(FinishParams p) {
@@ -585,7 +598,7 @@ __global__ void k_splitk_finish(FinishParams p) {
             }
         }
         float v;
-        if (p.gated) v = tc_act(p.act, g) * u;
+        if (p.gated) v = tc_gate(p.act, p.act_limit, g, u);
         else if (p.epilogue == TC_EPI_ADD) v = g + (p.bias ? p.bias[r] : 0.f);
         else v = tc_act(p.act, g + (p.bias ? p.bias[r] : 0.f));
         size_t o = t * p.ldo + r;
@@ -778,7 +791,7 @@ XR_EXPORT long long xr_gemm_tc_scratch_floats(int n, int n_out, int gated) {
 // in each quarter sixteen gate rows, then their sixteen up rows); n_out counts features and out is [n, n_out].
 // scratch: float32 workspace for products cut along K (xr_gemm_tc_scratch_floats bounds what is used); status:
 // device int, set non-zero if a wait gave up.
-XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* out, int out_dtype, int epilogue, int act,
+XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* out, int out_dtype, int epilogue, int act, float act_limit,
                          int n, int n_out, int K, long long ldx, long long ldo, float* scratch,
                          long long scratch_floats, int* status, int force_splits, int defer_finish, int* splits_used,
                          int w_packed, cudaStream_t stream) {
@@ -787,8 +800,8 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     if (epilogue != TC_EPI_STORE && epilogue != TC_EPI_ADD && epilogue != TC_EPI_GATED) return XR_ERR_ARG;
     if (epilogue == TC_EPI_ADD && (out_dtype != XR_F32 || act != TC_ACT_NONE)) return XR_ERR_ARG;
     if (out_dtype != XR_F32 && out_dtype != XR_BF16) return XR_ERR_ARG;
-    if (act != TC_ACT_NONE && act != TC_ACT_SILU && act != TC_ACT_GELU_TANH) return XR_ERR_ARG;
     const bool gated = epilogue == TC_EPI_GATED;
+    if (act != TC_ACT_NONE && act != TC_ACT_SILU && act != TC_ACT_GELU_TANH && !(act == TC_ACT_SWISH_CLAMP && gated)) return XR_ERR_ARG;
     if (gated && (!w_packed || bias != nullptr)) return XR_ERR_ARG;
     const TcPlan pl = plan_product(n, n_out, K, gated, force_splits, defer_finish != 0, scratch ? scratch_floats : 0);
     CUtensorMap mw, mx;
@@ -801,7 +814,7 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     if (pl.row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
     if (splits_used) *splits_used = splits;
     TcParams p{out, bias, scratch, status, ldo, n, n_out, K, splits, splits > 1 ? TC_EPI_PARTIAL : epilogue, out_dtype,
-               act, gated ? 1 : 0, pl.bn_eff, w_packed, pl.total_kb, pl.tok_tiles, pl.tok_tiles * ((pl.row_tiles + 1) / 2)};
+               act, act_limit, gated ? 1 : 0, pl.bn_eff, w_packed, pl.total_kb, pl.tok_tiles, pl.tok_tiles * ((pl.row_tiles + 1) / 2)};
     dim3 grid(pl.tok_tiles, pl.row_tiles, splits);
     int rc;
     if (pl.pair) {
@@ -821,7 +834,7 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
         }
     }
     if (rc != XR_OK || splits == 1 || defer_finish) return rc;      // deferred: the caller's next kernel sums the partials
-    FinishParams f{scratch, out, bias, ldo, n, n_out, splits, epilogue, out_dtype, gated ? 1 : 0, act};
+    FinishParams f{scratch, out, bias, ldo, n, n_out, splits, epilogue, out_dtype, gated ? 1 : 0, act, act_limit};
     size_t total = (size_t)n * n_out;
     const int most = xr_sm_count() * 8;
     int blocks = (int)((total + 255) / 256 < (size_t)most ? (total + 255) / 256 : most);
@@ -873,7 +886,7 @@ XR_EXPORT int xr_gemm_tc_noalloc(const void* X, const void* W, const float* bias
     // the status word must start at zero; the scratch needs no clearing (every partial that is read was
     // written by this call first)
     if (cudaMemsetAsync(g_noalloc_status_ptr[dev], 0, sizeof(int), stream) != cudaSuccess) return XR_ERR_LAUNCH;
-    int rc = xr_gemm_tc(X, W, bias, out, out_dtype, epilogue, TC_ACT_NONE, n, n_out, K, ldx, ldo, g_noalloc_scratch_ptr[dev],
+    int rc = xr_gemm_tc(X, W, bias, out, out_dtype, epilogue, TC_ACT_NONE, 0.f, n, n_out, K, ldx, ldo, g_noalloc_scratch_ptr[dev],
                         (long long)XR_NOALLOC_SCRATCH_FLOATS, g_noalloc_status_ptr[dev], want.splits, 0, nullptr, 0, stream);
     if (rc != XR_OK) return rc;
     if (status_out_host != nullptr) {

@@ -1,0 +1,190 @@
+// Matrix-memory recurrence (the mLSTM cell of xLSTM) with a stabilising running maximum, per request and head.
+//
+// State per (request slot, head): S [D][V], n [D], m (float32, zero when the slot is assigned).  For a token with
+// query q (times D^-1/2), key k, value v, pre-activations a_i, a_f of the gates and cap c:
+//   li = c tanh(a_i / c)                      (log of the input gate)
+//   lf = logsigmoid(c tanh(a_f / c))          (log of the forget gate)
+//   m' = max(lf + m, li);  f = exp(lf + m - m');  i = exp(li - m')
+//   S' = f S + i k v^T;    n' = f n + i k
+//   o  = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
+// Everything above is float32; q, k, v come from the projections in the activation dtype.
+//
+// Three kernels.  k_mlstm_gates walks a request's tokens once per head: m, f, i, n and the denominator of every token
+// (scalars per token and head), and leaves n and m in the state.  k_mlstm_scan walks them once per (head, slice of
+// 32 value columns) with S in shared memory, each thread updating its own cells, and writes o.  k_mlstm_out divides
+// each head's o by its root mean square, multiplies by the norm weight and the sigmoid of the output gate.
+// The walk is token by token in both, so the state after a token does not depend on how the tokens were cut into
+// steps, bit for bit.
+#include "common.cuh"
+#include <math.h>
+
+#define ML_VS 32          // value columns per block of the scan
+#define ML_RG 8           // row groups (warps) per block of the scan
+#define ML_CHUNK 16       // tokens whose q, k, v are staged together
+
+__device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// state layout per slot: [H][D * V + D + 1]
+__device__ __forceinline__ size_t ml_state_head(int D, int V) { return (size_t)D * V + D + 1; }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+k_mlstm_gates(const T* __restrict__ proj, long long ldp, int q_col, int k_col, const float* __restrict__ gates,
+              float* __restrict__ state, float* __restrict__ coef, const int* __restrict__ seg_start,
+              const int* __restrict__ seg_len, const int* __restrict__ seg_slot, int H, int D, int V, float cap) {
+    xr_pdl_launch();
+    __shared__ float scratch[33];
+    extern __shared__ float nsm[];              // n [D]
+    const int h = blockIdx.x, seg = blockIdx.y;
+    const int start = seg_start[seg], len = seg_len[seg], slot = seg_slot[seg];
+    xr_pdl_wait();
+    float* st = state + ((size_t)slot * H + h) * ml_state_head(D, V);
+    float* n_g = st + (size_t)D * V;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) nsm[d] = n_g[d];
+    float m = n_g[D];
+    const float qs = 1.0f / sqrtf((float)D);
+    __syncthreads();
+    for (int j = 0; j < len; j++) {
+        const int t = start + j;
+        const float ai = gates[(size_t)t * 2 * H + h], af = gates[(size_t)t * 2 * H + H + h];
+        const float li = cap * tanhf(ai / cap);
+        const float lf = ml_logsigmoid(cap * tanhf(af / cap));
+        const float m_new = fmaxf(lf + m, li);
+        const float f = expf(lf + m - m_new), i = expf(li - m_new);
+        const T* row = proj + (size_t)t * ldp;
+        float part = 0.f;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            const float kd = xr_to_f32<T>(row[k_col + h * D + d]);
+            const float qd = xr_to_f32<T>(row[q_col + h * D + d]) * qs;
+            const float nn = fmaf(f, nsm[d], i * kd);
+            nsm[d] = nn;
+            part = fmaf(nn, qd, part);
+        }
+        const float qn = xr_block_sum(part, scratch);
+        m = m_new;
+        if (threadIdx.x == 0) {
+            float* c = coef + ((size_t)t * H + h) * 3;
+            c[0] = f; c[1] = i; c[2] = fmaxf(fabsf(qn), expf(-m_new)) + 1e-6f;
+        }
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) n_g[d] = nsm[d];
+    if (threadIdx.x == 0) n_g[D] = m;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ML_VS * ML_RG)
+k_mlstm_scan(const T* __restrict__ proj, long long ldp, int q_col, int k_col, int v_col, const float* __restrict__ coef,
+             float* __restrict__ state, float* __restrict__ out, const int* __restrict__ seg_start,
+             const int* __restrict__ seg_len, const int* __restrict__ seg_slot, int H, int D, int V) {
+    xr_pdl_launch();
+    extern __shared__ float sm[];
+    float* S = sm;                                   // [D][ML_VS]
+    float* ks = S + (size_t)D * ML_VS;               // [ML_CHUNK][D]
+    float* qsm = ks + (size_t)ML_CHUNK * D;          // [ML_CHUNK][D]
+    float* vs = qsm + (size_t)ML_CHUNK * D;          // [ML_CHUNK][ML_VS]
+    float* red = vs + ML_CHUNK * ML_VS;              // [ML_CHUNK][ML_RG][ML_VS]
+    float* cf = red + ML_CHUNK * ML_RG * ML_VS;      // [ML_CHUNK][3]
+    const int col = threadIdx.x & (ML_VS - 1), rg = threadIdx.x / ML_VS;
+    const int v0 = blockIdx.x * ML_VS, h = blockIdx.y, seg = blockIdx.z;
+    const int start = seg_start[seg], len = seg_len[seg], slot = seg_slot[seg];
+    const bool col_ok = v0 + col < V;
+    xr_pdl_wait();
+    float* Sg = state + ((size_t)slot * H + h) * ml_state_head(D, V);
+    for (int d = rg; d < D; d += ML_RG) S[d * ML_VS + col] = col_ok ? Sg[(size_t)d * V + v0 + col] : 0.f;
+    const float qscale = 1.0f / sqrtf((float)D);
+    for (int j0 = 0; j0 < len; j0 += ML_CHUNK) {
+        const int cnt = min(ML_CHUNK, len - j0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < cnt * D; e += blockDim.x) {
+            const int j = e / D, d = e % D;
+            const T* row = proj + (size_t)(start + j0 + j) * ldp;
+            ks[j * D + d] = xr_to_f32<T>(row[k_col + h * D + d]);
+            qsm[j * D + d] = xr_to_f32<T>(row[q_col + h * D + d]) * qscale;
+        }
+        for (int e = threadIdx.x; e < cnt * ML_VS; e += blockDim.x) {
+            const int j = e / ML_VS, c = e % ML_VS;
+            vs[e] = v0 + c < V ? xr_to_f32<T>(proj[(size_t)(start + j0 + j) * ldp + v_col + h * V + v0 + c]) : 0.f;
+        }
+        for (int e = threadIdx.x; e < cnt * 3; e += blockDim.x) cf[e] = coef[((size_t)(start + j0 + e / 3) * H + h) * 3 + e % 3];
+        __syncthreads();
+        for (int j = 0; j < cnt; j++) {
+            const float f = cf[j * 3], iv = cf[j * 3 + 1] * vs[j * ML_VS + col];
+            float num = 0.f;
+            for (int d = rg; d < D; d += ML_RG) {
+                const float s = fmaf(f, S[d * ML_VS + col], iv * ks[j * D + d]);
+                S[d * ML_VS + col] = s;
+                num = fmaf(s, qsm[j * D + d], num);
+            }
+            red[(j * ML_RG + rg) * ML_VS + col] = num;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < cnt * ML_VS; e += blockDim.x) {
+            const int j = e / ML_VS, c = e % ML_VS;
+            if (v0 + c >= V) continue;
+            float num = 0.f;
+#pragma unroll
+            for (int r = 0; r < ML_RG; r++) num += red[(j * ML_RG + r) * ML_VS + c];
+            out[(size_t)(start + j0 + j) * H * V + (size_t)h * V + v0 + c] = num / cf[j * 3 + 2];
+        }
+    }
+    __syncthreads();
+    if (col_ok)
+        for (int d = rg; d < D; d += ML_RG) Sg[(size_t)d * V + v0 + col] = S[d * ML_VS + col];
+}
+
+// o [n][H][V] float32 -> y [n][H * V] (activation dtype): o / rms(o over the head) * w * sigmoid(g); one warp per (token, head)
+template <typename T>
+__global__ void __launch_bounds__(128)
+k_mlstm_out(const float* __restrict__ o, const T* __restrict__ proj, long long ldp, int g_col, const float* __restrict__ w,
+            T* __restrict__ y, int n, int H, int V, float eps) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long idx = (long long)blockIdx.x * 4 + warp;
+    if (idx >= (long long)n * H) return;
+    const int t = (int)(idx / H), h = (int)(idx % H);
+    const float* src = o + ((size_t)t * H + h) * V;
+    float ss = 0.f;
+    for (int i = lane; i < V; i += 32) ss = fmaf(src[i], src[i], ss);
+    ss = xr_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+    const T* g = proj + (size_t)t * ldp + g_col + (size_t)h * V;
+    T* dst = y + (size_t)t * H * V + (size_t)h * V;
+    for (int i = lane; i < V; i += 32) {
+        const float gate = 1.0f / (1.0f + expf(-xr_to_f32<T>(g[i])));
+        dst[i] = xr_from_f32<T>(src[i] * inv * w[h * V + i] * gate);
+    }
+}
+
+// proj [n][ldp] (activation dtype): q at q_col [H][D], k at k_col [H][D], v at v_col [H][V], output gate at g_col [H][V];
+// gates [n][2H] float32 (input-gate pre-activations, then forget-gate ones, biases included);
+// state [slots][H][D*V + D + 1] float32;  coef [n][H][3], o [n][H][V]: float32 scratch;  y [n][H*V] activation dtype.
+XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, int k_col, int v_col, int g_col, const float* gates,
+                       float* state, float* coef, float* o, const float* norm_w, void* y, const int* seg_start,
+                       const int* seg_len, const int* seg_slot, int n, int n_seg, int H, int D, int V, float cap, float eps,
+                       cudaStream_t stream) {
+    if (n < 1 || n_seg < 1 || H < 1 || D < 1 || V < 1 || !(cap > 0.f) || n_seg > 65535 || H > 65535) return XR_ERR_ARG;
+    const size_t smem_g = (size_t)D * sizeof(float);
+    const size_t smem_s = ((size_t)D * ML_VS + 2 * (size_t)ML_CHUNK * D + ML_CHUNK * ML_VS + ML_CHUNK * ML_RG * ML_VS + ML_CHUNK * 3) * sizeof(float);
+    if (smem_g > 48 * 1024 || smem_s > 220 * 1024) return XR_ERR_ARG;
+    dim3 gg(H, n_seg), gs((V + ML_VS - 1) / ML_VS, H, n_seg);
+    const long long warps = (long long)n * H;
+    const unsigned gb = (unsigned)((warps + 3) / 4);
+#define ML(T)                                                                                                                         \
+    do {                                                                                                                              \
+        if (smem_s > 48 * 1024 &&                                                                                                     \
+            cudaFuncSetAttribute(k_mlstm_scan<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s) != cudaSuccess)           \
+            return XR_ERR_LAUNCH;                                                                                                     \
+        xr_launch((k_mlstm_gates<T>), gg, dim3(256), smem_g, stream, (const T*)proj, ldp, q_col, k_col, gates, state, coef, seg_start, \
+                  seg_len, seg_slot, H, D, V, cap);                                                                                   \
+        xr_launch((k_mlstm_scan<T>), gs, dim3(ML_VS * ML_RG), smem_s, stream, (const T*)proj, ldp, q_col, k_col, v_col,                \
+                  (const float*)coef, state, o, seg_start, seg_len, seg_slot, H, D, V);                                               \
+        xr_launch((k_mlstm_out<T>), dim3(gb), dim3(128), 0, stream, (const float*)o, (const T*)proj, ldp, g_col, norm_w, (T*)y, n, H, \
+                  V, eps);                                                                                                            \
+    } while (0)
+    if (dtype == XR_F32) ML(float);
+    else if (dtype == XR_BF16) ML(__nv_bfloat16);
+    else return XR_ERR_ARG;
+#undef ML
+    return xr_launch_status();
+}

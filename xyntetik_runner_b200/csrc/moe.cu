@@ -1,0 +1,247 @@
+// Routed experts (mixture of experts): the choice of experts per token, the order of (token, choice) pairs by expert,
+// the experts' products over the rows that chose them, and the weighted sum back into the token's stream.
+//
+//   z = W_router h (float32, a product of the caller);  the `top` largest z are chosen (ties: the lower index),
+//   weights = softmax over the chosen z only;  out[t] += sum_j weight_j * expert_{e_j}(h[t]).
+// An expert is a gated feed-forward: y = gate_act(W_gate h, W_up h), then W_down y (see xr_gate below for the
+// activations).  No step reads anything back to the host: the plan of who computes what is made on the device, and
+// the grids are sized for the worst case (every tile index beyond the plan's count returns at once).
+#include "common.cuh"
+#include <math.h>
+
+// ---------------------------------------------------------------------------------------------
+// Choice: one warp per token.  ids [n][top] int32, wts [n][top] float32 (in the order of descending z).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+k_route_topk(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int n, int E, int top) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= n) return;
+    const float* row = z + (size_t)t * E;
+    float best0 = 0.f, sum = 0.f;
+    int last_e = -1;
+    float last_v = INFINITY;
+    // the j-th choice: the largest value that comes after the (j-1)-th in the order (value descending, index ascending)
+    for (int j = 0; j < top; j++) {
+        float bv = -INFINITY;
+        int be = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = row[e];
+            const bool after = v < last_v || (v == last_v && e > last_e);
+            if (after && (v > bv || (v == bv && e < be))) { bv = v; be = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+        }
+        if (j == 0) best0 = bv;
+        const float p = expf(bv - best0);
+        sum += p;
+        if (lane == 0) { ids[(size_t)t * top + j] = be; wts[(size_t)t * top + j] = p; }
+        last_v = bv; last_e = be;
+    }
+    __syncwarp();
+    if (lane < top) wts[(size_t)t * top + lane] /= sum;
+    for (int j = 32 + lane; j < top; j += 32) wts[(size_t)t * top + j] /= sum;
+}
+
+XR_EXPORT int xr_route_topk(const float* z, int* ids, float* wts, int n, int E, int top, cudaStream_t stream) {
+    if (n < 1 || E < 1 || top < 1 || top > E) return XR_ERR_ARG;
+    xr_launch(k_route_topk, dim3((n + 3) / 4), dim3(128), 0, stream, z, ids, wts, n, E, top);
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Plan, one block: rows = the n * top pairs sorted by expert.
+//   row_pair [pairs]: the pair (t * top + j) that row r computes;  pair_row [pairs]: the inverse;
+//   tiles of MOE_TM rows that never span two experts: tile_info [max_tiles][3] = (expert, first row, rows), and
+//   plan_counts[0] = number of tiles.  max_tiles = pairs / MOE_TM + E + 1 always suffices.
+// Which row a pair gets among its expert's rows depends on the order in which threads arrive; a row's result does not.
+// ---------------------------------------------------------------------------------------------
+#define MOE_TM 64
+#define MOE_MAX_E 1024
+
+__global__ void __launch_bounds__(1024)
+k_moe_plan(const int* __restrict__ ids, int* __restrict__ row_pair, int* __restrict__ pair_row, int* __restrict__ tile_info,
+           int* __restrict__ plan_counts, int pairs, int E) {
+    xr_pdl_launch();
+    __shared__ int count[MOE_MAX_E], first[MOE_MAX_E], cursor[MOE_MAX_E], tile0[MOE_MAX_E + 1];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    xr_pdl_wait();
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < E; e++) {
+            first[e] = at; cursor[e] = at; tile0[e] = tiles;
+            at += count[e];
+            tiles += (count[e] + MOE_TM - 1) / MOE_TM;
+        }
+        tile0[E] = tiles;
+        plan_counts[0] = tiles;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int r = atomicAdd(&cursor[ids[p]], 1);
+        row_pair[r] = p;
+        pair_row[p] = r;
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int nt = tile0[e + 1] - tile0[e];
+        for (int i = 0; i < nt; i++) {
+            int* ti = tile_info + (size_t)(tile0[e] + i) * 3;
+            ti[0] = e; ti[1] = first[e] + i * MOE_TM; ti[2] = min(MOE_TM, count[e] - i * MOE_TM);
+        }
+    }
+}
+
+XR_EXPORT int xr_moe_plan(const int* ids, int* row_pair, int* pair_row, int* tile_info, int* plan_counts, int pairs, int E,
+                          cudaStream_t stream) {
+    if (pairs < 1 || E < 1 || E > MOE_MAX_E) return XR_ERR_ARG;
+    xr_launch(k_moe_plan, dim3(1), dim3(1024), 0, stream, ids, row_pair, pair_row, tile_info, plan_counts, pairs, E);
+    return xr_launch_status();
+}
+
+XR_EXPORT int xr_moe_tile_rows() { return MOE_TM; }
+
+// ---------------------------------------------------------------------------------------------
+// The experts' products over the planned tiles, float32 FMA, k in ascending order for every result.
+//  first product (gated = 1): rows gather their token's h (row_pair[r] / top); W = [E][2F][K] (an expert's gate rows,
+//    then its up rows); out Y [pairs][F] in the activation dtype = gate_act(h . w_gate_f, h . w_up_f).
+//  second product (gated = 0): rows read Y [pairs][K = F]; W = [E][N][K]; out Z [pairs][N] float32.
+// Tile: 64 rows x 64 columns (gated: 32 features, gate and up side by side), 256 threads with 4 x 4 results each.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float moe_gate(int act, float limit, float g, float u) {
+    if (act == 3) {                  // g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    if (act == 1) return (g < -80.0f ? 0.0f : g / (1.0f + expf(-g))) * u;
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g))) * u;
+    return g * u;
+}
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+k_moe_gemm(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, TO* __restrict__ out, long long ldo,
+           const int* __restrict__ row_pair, const int* __restrict__ tile_info, const int* __restrict__ plan_counts,
+           int top, int N, int K, int gated, int act, float limit) {
+    xr_pdl_launch();
+    __shared__ float As[16][64 + 1], Ws[16][64 + 1];
+    __shared__ int src_row[64];
+    xr_pdl_wait();
+    if ((int)blockIdx.x >= plan_counts[0]) return;
+    const int e = tile_info[blockIdx.x * 3], r0 = tile_info[blockIdx.x * 3 + 1], rows = tile_info[blockIdx.x * 3 + 2];
+    const int cols = gated ? 32 : 64;                 // output columns (features) per tile
+    const int c0 = blockIdx.y * cols;
+    const TW* We = W + (size_t)e * (gated ? 2 : 1) * N * K;
+    if (threadIdx.x < 64) {
+        int r = threadIdx.x;
+        src_row[r] = r < rows ? (gated ? row_pair[r0 + r] / top : r0 + r) : -1;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+            const int kk = i & 15, r = i >> 4, k = k0 + kk, s = src_row[r];
+            As[kk][r] = (s >= 0 && k < K) ? xr_to_f32<TA>(A[(size_t)s * lda + k]) : 0.f;
+        }
+        for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+            const int kk = i & 15, c = i >> 4, k = k0 + kk;
+            // gated: columns 0..31 are gate rows c0 + c, columns 32..63 the up rows of the same features
+            const int wrow = gated ? (c < 32 ? c0 + c : N + c0 + c - 32) : c0 + c;
+            const bool ok = k < K && (gated ? (c0 + (c & 31) < N) : (c0 + c < N));
+            Ws[kk][c] = ok ? xr_to_f32<TW>(We[(size_t)wrow * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; kk++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { a[i] = As[kk][ty + 16 * i]; b[i] = Ws[kk][tx + 16 * i]; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int r = ty + 16 * i;
+        if (r >= rows) continue;
+        TO* orow = out + (size_t)(r0 + r) * ldo;
+        if (gated) {
+            // this thread's columns tx, tx + 16 are gate sums, tx + 32, tx + 48 the up sums of the same two features
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int f = c0 + tx + 16 * j;
+                if (f < N) orow[f] = xr_from_f32<TO>(moe_gate(act, limit, acc[i][j], acc[i][j + 2]));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int c = c0 + tx + 16 * j;
+                if (c < N) orow[c] = xr_from_f32<TO>(acc[i][j]);
+            }
+        }
+    }
+}
+
+// dtype: of the activations (A of the first product, Y); w_dtype: of the experts' matrices.
+XR_EXPORT int xr_moe_gemm(const void* A, int a_dtype, long long lda, const void* W, int w_dtype, void* out, int out_dtype,
+                          long long ldo, const int* row_pair, const int* tile_info, const int* plan_counts, int max_tiles,
+                          int top, int N, int K, int gated, int act, float limit, cudaStream_t stream) {
+    if (max_tiles < 1 || N < 1 || K < 1 || top < 1 || act < 0 || act > 3) return XR_ERR_ARG;
+    const int cols = gated ? 32 : 64;
+    dim3 grid(max_tiles, (N + cols - 1) / cols);
+    if (grid.y > 65535) return XR_ERR_ARG;
+    typedef __nv_bfloat16 bf;
+#define MG(TA, TW, TO) xr_launch((k_moe_gemm<TA, TW, TO>), grid, dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, (TO*)out, ldo, \
+                                 row_pair, tile_info, plan_counts, top, N, K, gated, act, limit)
+    const int key = a_dtype * 4 + w_dtype * 2 + out_dtype;
+    switch (key) {
+        case XR_BF16 * 4 + XR_BF16 * 2 + XR_BF16: MG(bf, bf, bf); break;
+        case XR_BF16 * 4 + XR_BF16 * 2 + XR_F32: MG(bf, bf, float); break;
+        case XR_F32 * 4 + XR_BF16 * 2 + XR_F32: MG(float, bf, float); break;
+        case XR_F32 * 4 + XR_F32 * 2 + XR_F32: MG(float, float, float); break;
+        case XR_BF16 * 4 + XR_F32 * 2 + XR_BF16: MG(bf, float, bf); break;
+        case XR_BF16 * 4 + XR_F32 * 2 + XR_F32: MG(bf, float, float); break;
+        default: return XR_ERR_ARG;
+    }
+#undef MG
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// d[t][c] += sum_j wts[t][j] * Z[pair_row[t * top + j]][c], j ascending (float32).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_moe_combine(float* __restrict__ d, const float* __restrict__ Z, const float* __restrict__ wts, const int* __restrict__ pair_row,
+              int n, int width, int top) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const size_t total = (size_t)n * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width, c = i % width;
+        float s = 0.f;
+        for (int j = 0; j < top; j++) s = fmaf(wts[t * top + j], Z[(size_t)pair_row[t * top + j] * width + c], s);
+        d[i] += s;
+    }
+}
+
+XR_EXPORT int xr_moe_combine(float* d, const float* Z, const float* wts, const int* pair_row, int n, int width, int top,
+                             cudaStream_t stream) {
+    if (n < 1 || width < 1 || top < 1) return XR_ERR_ARG;
+    const size_t total = (size_t)n * width;
+    int blocks = (int)((total + 255) / 256 < (size_t)xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
+    xr_launch(k_moe_combine, dim3(blocks), dim3(256), 0, stream, d, Z, wts, pair_row, n, width, top);
+    return xr_launch_status();
+}

@@ -149,12 +149,12 @@ class Engine:
         max_req = p.max_request_tokens or min(plan.max_positions, n_pages * p.page_size)
         self.cache = CacheManager([g.spec for g in self.model.groups] or [], n_pages, p.page_size,
                                   p.max_requests, max_req)
-        # device arrays of keys and values: [page][layer in group][K|V][kv head][token in page][head_dim].  One page
+        # device arrays of keys and values: [page][layer in group][K|V (the group's planes)][kv head][token in page][head_dim].  One page
         # more than the pool hands out: the rows that fill a decode step up to a repeating size write there.
         self.kv: List[torch.Tensor] = []
         self._filler_page = n_pages
         for g in self.model.groups:
-            self.kv.append(torch.zeros((n_pages + 1, g.n_layers, 2, g.kv_heads, p.page_size, g.head_dim),
+            self.kv.append(torch.zeros((n_pages + 1, g.n_layers, g.planes, g.kv_heads, p.page_size, g.head_dim),
                                        dtype=self.act_dtype, device=self.device))
         self._cache_layer: Dict[int, tuple] = {}
         for lay in self.model.layers:
@@ -408,8 +408,16 @@ class Engine:
         plan = self.plan
         x = ctx.buf("residual", (ctx.n, plan.width), torch.float32)
         plan.embedding.forward(ctx, ctx.token_ids, x)
+        x0 = None
+        if plan.keeps_embedding():
+            # the embedding's output is kept for the parts that join it to the stream again
+            x0 = ctx.buf("embedding_out", (ctx.n, plan.width), torch.float32)
+            plan.embedding.forward(ctx, ctx.token_ids, x0)
         for lay in self.model.layers:
-            plan.blocks[plan.schedule[lay.entry].layer].forward(ctx, x, lay)
+            entry = plan.schedule[lay.entry]
+            if entry.before is not None:
+                plan.stream_parts[entry.before].forward(ctx, x, x0)
+            plan.blocks[entry.layer].forward(ctx, x, lay)
         if ctx.n_rows == 0:
             ctx.materialize(x)
             return torch.empty((0, plan.vocab_size), dtype=torch.float32, device=self.device)

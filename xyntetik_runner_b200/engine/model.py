@@ -11,13 +11,13 @@ schedule's cache entries into groups of equal need.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 import torch
 
 from ..cache.pages import GroupSpec
-from ..parts.base import Block, KVNeed, Norm, Runtime, StateNeed
+from ..parts.base import Block, KVNeed, Norm, Part, Runtime, StateNeed
 from ..parts.embedding import Embedding, Head
 from ..weights.loader import TensorSource, TensorSpec, load_tensors
 
@@ -26,6 +26,7 @@ from ..weights.loader import TensorSource, TensorSpec, load_tensors
 class ScheduleEntry:
     layer: int                         # index into ModelPlan.blocks
     cache_from: Optional[int] = None   # index of an earlier schedule entry whose keys/values this one reads
+    before: Optional[int] = None       # index into ModelPlan.stream_parts: run on the residual stream right before this entry
 
 
 @dataclass
@@ -40,9 +41,16 @@ class ModelPlan:
     max_positions: int
     stop_ids: Tuple[int, ...] = ()
     bos_id: Optional[int] = None
+    # parts that act on the residual stream between layers (``forward(ctx, x, x0)``, x0 the embedding's output): a
+    # schedule entry names one with `before`
+    stream_parts: List[Part] = field(default_factory=list)
 
     def parts(self):
-        return [self.embedding] + list(self.blocks) + [self.final_norm, self.head]
+        return [self.embedding] + list(self.blocks) + list(self.stream_parts) + [self.final_norm, self.head]
+
+    def keeps_embedding(self) -> bool:
+        """Whether a step must keep the embedding's output beside the residual stream."""
+        return any(e.before is not None for e in self.schedule)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         out: Dict[str, TensorSpec] = {}
@@ -57,12 +65,14 @@ class ModelPlan:
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.blocks)):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
+            if e.before is not None and not (0 <= e.before < len(self.stream_parts)):
+                raise ValueError(f"schedule entry {i} names stream part {e.before}, the model has {len(self.stream_parts)}")
             if e.cache_from is not None:
                 if not (0 <= e.cache_from < i) or self.schedule[e.cache_from].cache_from is not None:
                     raise ValueError(f"schedule entry {i}: cache_from must name an earlier entry that owns a cache")
                 a = self.blocks[e.layer].mixer.kv_need()
                 b = self.blocks[self.schedule[e.cache_from].layer].mixer.kv_need()
-                if a is None or b is None or (a.kv_heads, a.head_dim) != (b.kv_heads, b.head_dim):
+                if a is None or b is None or (a.kv_heads, a.head_dim, a.planes) != (b.kv_heads, b.head_dim, b.planes):
                     raise ValueError(f"schedule entry {i}: cannot read the cache of entry {e.cache_from} (geometry differs)")
 
 
@@ -82,6 +92,7 @@ class CacheGroupLayout:
     kv_heads: int
     head_dim: int
     n_layers: int = 0
+    planes: int = 2
 
 
 class LoadedModel:
@@ -97,7 +108,7 @@ class LoadedModel:
         self.groups: List[CacheGroupLayout] = []
         self.layers: List[LayerRuntime] = []
         self.state_needs: List[Tuple[int, StateNeed]] = []
-        keys: Dict[Tuple[int, int, Optional[int]], int] = {}
+        keys: Dict[Tuple[int, int, Optional[int], int], int] = {}
         for i, e in enumerate(plan.schedule):
             mixer = plan.blocks[e.layer].mixer
             lay = LayerRuntime(entry=i)
@@ -107,12 +118,12 @@ class LoadedModel:
                     src = self.layers[e.cache_from]
                     lay.group, lay.layer_in_group, lay.writes_cache = src.group, src.layer_in_group, False
                 else:
-                    key = (need.kv_heads, need.head_dim, need.window)
+                    key = (need.kv_heads, need.head_dim, need.window, need.planes)
                     if key not in keys:
                         keys[key] = len(self.groups)
                         name = "full" if need.window is None else f"window{need.window}"
-                        self.groups.append(CacheGroupLayout(GroupSpec(f"{name}:{need.kv_heads}x{need.head_dim}", need.window),
-                                                            need.kv_heads, need.head_dim))
+                        self.groups.append(CacheGroupLayout(GroupSpec(f"{name}:{need.planes}x{need.kv_heads}x{need.head_dim}", need.window),
+                                                            need.kv_heads, need.head_dim, planes=need.planes))
                     g = keys[key]
                     lay.group, lay.layer_in_group, lay.writes_cache = g, self.groups[g].n_layers, True
                     self.groups[g].n_layers += 1
@@ -122,10 +133,11 @@ class LoadedModel:
             self.layers.append(lay)
 
     def kv_bytes_per_token(self, elem_size: int) -> int:
-        return sum(2 * g.kv_heads * g.head_dim * g.n_layers * elem_size for g in self.groups)
+        return sum(g.planes * g.kv_heads * g.head_dim * g.n_layers * elem_size for g in self.groups)
 
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights one step reads: every scheduled block once, the final norm and the head
         (the embedding table is read by row only)."""
         total = sum(self.plan.blocks[e.layer].weight_bytes() for e in self.plan.schedule)
+        total += sum(self.plan.stream_parts[e.before].weight_bytes() for e in self.plan.schedule if e.before is not None)
         return total + self.plan.final_norm.weight_bytes() + self.plan.head.weight_bytes()

@@ -47,14 +47,14 @@ _vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 
 def _declare(L: ctypes.CDLL) -> None:
     sig = {
-        "xr_embed": [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
+        "xr_embed": [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _f, _vp],
         "xr_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
-        "xr_act_mul": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
+        "xr_act_mul": [_vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
         "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
         "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
-        "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
+        "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
         "xr_finish_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
@@ -69,6 +69,18 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_sample_one_block": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_logprob": [_vp, _ll, _i, _i, _vp, _vp, _vp],
         "xr_random_normal": [_vp, _i, _ll, ctypes.c_ulonglong, ctypes.c_ulonglong, _f, _f, _vp],
+        "xr_scaled_add": [_vp, _vp, _f, _i, _i, _vp],
+        "xr_concat_cast": [_vp, _vp, _vp, _i, _i, _i, _vp],
+        "xr_softcap": [_vp, _f, _ll, _vp],
+        "xr_latent_prep": [_vp, _i, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_head_matmul": [_vp, _i, _ll, _i, _vp, _i, _ll, _ll, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp],
+        "xr_latent_attention": [_vp, _vp, _i, _ll, _i, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_mlstm": [_vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
+        "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
+        "xr_moe_plan": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+        "xr_moe_tile_rows": [],
+        "xr_moe_gemm": [_vp, _i, _ll, _vp, _i, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -122,15 +134,15 @@ def _count(n: int = 1) -> None:
 
 
 # ---------------------------------------------------------------------------
-def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, feed: Optional[torch.Tensor] = None) -> None:
-    """x[t] = table[ids[t]] widened to float32; ids outside the table read row 0.  With `feed` (int32 on the
-    device), ids[t] = -(1 + j) reads token feed[j]."""
+def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, feed: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """x[t] = table[ids[t]] widened to float32, times `scale`; ids outside the table read row 0.  With `feed` (int32
+    on the device), ids[t] = -(1 + j) reads token feed[j]."""
     _dev(table, ids, x, feed)
     n, d = x.shape
     assert ids.dtype == torch.int32 and ids.numel() >= n and x.dtype == torch.float32 and table.shape[1] == d
     assert feed is None or feed.dtype == torch.int32
     _check(lib().xr_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), _ptr(feed),
-                          0 if feed is None else feed.numel(), x.data_ptr(), n, d, table.shape[0], _stream()), "embed")
+                          0 if feed is None else feed.numel(), x.data_ptr(), n, d, table.shape[0], float(scale), _stream()), "embed")
     _count()
 
 
@@ -162,16 +174,19 @@ def rope_store(qkv: torch.Tensor, positions, tok_seg, block_tables, inv_freq: Op
     _count()
 
 
-ACT_NONE, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
-ACTIVATIONS = {"none": ACT_NONE, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SWISH_CLAMP = 0, 1, 2, 3
+# "swish_clamp" exists for gated products only and takes a `limit`: with g' = min(g, limit) and u' = u clamped to
+# [-limit, limit] the product stores g' sigmoid(1.702 g') (u' + 1).
+ACTIVATIONS = {"none": ACT_NONE, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "swish_clamp": ACT_SWISH_CLAMP}
 
 
-def act_mul(gu: torch.Tensor, h: torch.Tensor, act: int = ACT_SILU, gated: bool = True) -> None:
-    """Gated: h[t][f] = act(gu[t][f]) * gu[t][F + f] for gu [n, 2F]; ungated: h = act(gu) for gu [n, F] (h may be gu)."""
+def act_mul(gu: torch.Tensor, h: torch.Tensor, act: int = ACT_SILU, gated: bool = True, limit: float = 0.0) -> None:
+    """Gated: h[t][f] = act(gu[t][f]) * gu[t][F + f] for gu [n, 2F] (ACT_SWISH_CLAMP: see ACTIVATIONS); ungated:
+    h = act(gu) for gu [n, F] (h may be gu)."""
     _dev(gu, h)
     n, F = h.shape
     assert gu.shape == (n, 2 * F if gated else F) and gu.dtype == h.dtype
-    _check(lib().xr_act_mul(gu.data_ptr(), h.data_ptr(), dtype_code(h.dtype), n, F, int(act), int(gated), _stream()), "act_mul")
+    _check(lib().xr_act_mul(gu.data_ptr(), h.data_ptr(), dtype_code(h.dtype), n, F, int(act), int(gated), float(limit), _stream()), "act_mul")
     _count()
 
 
@@ -415,7 +430,7 @@ _SPLITS_USED = ctypes.c_int(1)           # where xr_gemm_tc says how it cut the 
 _SPLITS_USED_REF = ctypes.byref(_SPLITS_USED)
 
 
-def _gemm_tc(x, w, out, bias, epilogue, act, force_splits, defer, packed_rows):
+def _gemm_tc(x, w, out, bias, epilogue, act, force_splits, defer, packed_rows, act_limit=0.0):
     n, k = x.shape
     gated = epilogue == EPI_GATED
     if packed_rows is not None:
@@ -433,7 +448,7 @@ def _gemm_tc(x, w, out, bias, epilogue, act, force_splits, defer, packed_rows):
     assert not defer or not gated
     ws = workspace(x.device)
     at, room = ws.room()
-    _check(lib().xr_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), dtype_code(out.dtype), epilogue, int(act),
+    _check(lib().xr_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), dtype_code(out.dtype), epilogue, int(act), float(act_limit),
                             n, n_out, k, x.stride(0), out.stride(0), at, room,
                             ws.status_ptr, force_splits, int(defer), _SPLITS_USED_REF,
                             int(packed_rows is not None), _stream()), "gemm_tc")
@@ -446,13 +461,14 @@ def _gemm_tc(x, w, out, bias, epilogue, act, force_splits, defer, packed_rows):
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            epilogue: int = EPI_STORE, force_splits: int = 0, packed_rows: Optional[int] = None, act: Optional[int] = None) -> int:
+            epilogue: int = EPI_STORE, force_splits: int = 0, packed_rows: Optional[int] = None, act: Optional[int] = None,
+            act_limit: float = 0.0) -> int:
     """bfloat16 product on tcgen05.  EPI_STORE: out[t][r] = act(x.w + bias); EPI_ADD: float32 out += x.w + bias;
     EPI_GATED: w from ``pack_weight(w, halves=2)``, out[t][f] = act(x.w_gate[f]) * (x.w_up[f]) (act defaults to SiLU).
     Returns the number of K splits used."""
     if act is None:
         act = ACT_SILU if epilogue == EPI_GATED else ACT_NONE
-    return _gemm_tc(x, w, out, bias, epilogue, act, force_splits, False, packed_rows)
+    return _gemm_tc(x, w, out, bias, epilogue, act, force_splits, False, packed_rows, act_limit)
 
 
 def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -582,4 +598,158 @@ def attention_tc(qkv: torch.Tensor, out: torch.Tensor, seg_start, seg_len, seg_p
                                  seg_pos0.data_ptr(), block_tables.data_ptr(), status.data_ptr(), qkv.stride(0), n, n_seg,
                                  H, K, hd, max_pages, page_size, window, float(scale), max_seg_len, row_tiles, group[1], group[2],
                                  group[3], _stream()), "attention_tc")
+    _count()
+
+
+# ---------------------------------------------------------------------------
+# Kernels of blocks that run their sublayers side by side, of joined streams and of capped logits
+def scaled_add(x: torch.Tensor, d: torch.Tensor, m: float) -> None:
+    """x += m * d on float32 streams."""
+    _dev(x, d)
+    assert x.dtype == torch.float32 and d.dtype == torch.float32 and x.shape == d.shape
+    _check(lib().xr_scaled_add(x.data_ptr(), d.data_ptr(), float(m), x.shape[0], x.shape[1], _stream()), "scaled_add")
+    _count()
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t]; b[t]] of two float32 streams [n, width], in out's dtype."""
+    _dev(a, b, out)
+    n, width = a.shape
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and b.shape == a.shape and out.shape == (n, 2 * width)
+    _check(lib().xr_concat_cast(a.data_ptr(), b.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n, width, _stream()), "concat_cast")
+    _count()
+
+
+def softcap(z: torch.Tensor, cap: float) -> None:
+    """z <- cap * tanh(z / cap) in place on float32 logits."""
+    _dev(z)
+    assert z.dtype == torch.float32
+    _check(lib().xr_softcap(z.data_ptr(), float(cap), z.numel(), _stream()), "softcap")
+    _count()
+
+
+# ---------------------------------------------------------------------------
+# Latent attention (csrc/latent_attention.cu)
+def latent_prep(proj: torch.Tensor, down_col: int, positions, tok_seg, block_tables, freq: Optional[torch.Tensor],
+                norm_w: torch.Tensor, cache_ptr: Optional[int], page_stride: int, H: int, D: int, R: int, C: int,
+                rot_dims: int, max_pages: int, page_size: int, eps: float) -> None:
+    """Rotate the rotated part of every head's query in `proj` in place; write the token's cache row
+    [normed latent (C) | rotated key part (R)] (cache_ptr None: write nothing).  freq: float64 [rot_dims / 2]."""
+    _dev(positions, tok_seg, block_tables, freq, norm_w)
+    assert proj.stride(1) == 1 and proj.is_cuda
+    assert freq is None or freq.dtype == torch.float64
+    assert norm_w.dtype == torch.float32 and norm_w.numel() == C and proj.shape[1] >= down_col + C + R
+    _check(lib().xr_latent_prep(proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), down_col, positions.data_ptr(),
+                                tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(freq), norm_w.data_ptr(), cache_ptr, page_stride,
+                                proj.shape[0], H, D, R, C, rot_dims, max_pages, page_size, float(eps), _stream()), "latent_prep")
+    _count()
+
+
+def head_matmul(inp: torch.Tensor, in_col: int, head_in: int, w: torch.Tensor, transposed: bool, out: torch.Tensor,
+                n: int, H: int, Kd: int, J: int, gate: Optional[torch.Tensor] = None, gate_col: int = 0) -> None:
+    """out[t, h, j] = sum_k inp[t, in_col + h * head_in + k] * W_h(k, j) (* sigmoid(gate[t, gate_col + h])), float32 sums.
+    w [H * Kd, J] with W_h(k, j) = w[h * Kd + k, j], or `transposed`: w [H * J, Kd] with W_h(k, j) = w[h * J + j, k].
+    out is [n, H * J] (any of the two dtypes)."""
+    assert w.is_contiguous() and inp.stride(1) == 1 and out.is_contiguous() and out.shape == (n, H * J)
+    assert tuple(w.shape) == ((H * J, Kd) if transposed else (H * Kd, J))
+    es = inp.element_size()
+    w_head, w_k, w_j = (J * Kd, 1, Kd) if transposed else (Kd * J, J, 1)
+    gptr = None if gate is None else gate.data_ptr() + gate_col * gate.element_size()
+    _check(lib().xr_head_matmul(inp.data_ptr() + in_col * es, dtype_code(inp.dtype), inp.stride(0), head_in, w.data_ptr(),
+                                dtype_code(w.dtype), w_head, w_k, w_j, out.data_ptr(), dtype_code(out.dtype), out.stride(0),
+                                gptr, 0 if gate is None else dtype_code(gate.dtype), 0 if gate is None else gate.stride(0),
+                                n, H, Kd, J, _stream()), "head_matmul")
+    _count()
+
+
+def latent_attention(ql: torch.Tensor, proj: torch.Tensor, qr_col: int, head_qr: int, out: torch.Tensor, cache_ptr: int,
+                     page_stride: int, positions, tok_seg, block_tables, H: int, C: int, R: int, max_pages: int,
+                     page_size: int, scale: float) -> None:
+    """Causal softmax attention of every token over its request's cached rows [latent (C) | rotated key part (R)]:
+    ql [n, H * C] float32 (queries in the latent space), rotated query parts in `proj` (head h at column
+    qr_col + h * head_qr), out [n, H * C] float32 = sum_j a_j latent_j."""
+    _dev(ql, out, positions, tok_seg, block_tables)
+    n = ql.shape[0]
+    assert ql.dtype == torch.float32 and out.dtype == torch.float32 and ql.shape == (n, H * C) and out.shape == (n, H * C)
+    _check(lib().xr_latent_attention(ql.data_ptr(), proj.data_ptr() + qr_col * proj.element_size(), dtype_code(proj.dtype),
+                                     proj.stride(0), head_qr, out.data_ptr(), cache_ptr, page_stride, positions.data_ptr(),
+                                     tok_seg.data_ptr(), block_tables.data_ptr(), n, H, C, R, max_pages, page_size, float(scale),
+                                     _stream()), "latent_attention")
+    _count()
+
+
+# ---------------------------------------------------------------------------
+# Matrix-memory recurrence (csrc/mlstm.cu)
+def mlstm_state_floats(H: int, D: int, V: int) -> int:
+    return H * (D * V + D + 1)
+
+
+def mlstm(proj: torch.Tensor, cols, gates: torch.Tensor, state: torch.Tensor, coef: torch.Tensor, o: torch.Tensor,
+          norm_w: torch.Tensor, y: torch.Tensor, seg_start, seg_len, seg_slot, n_seg: int, H: int, D: int, V: int,
+          cap: float, eps: float) -> None:
+    """The recurrence over the step's tokens, request by request, from and into `state` [slots, H * (D V + D + 1)].
+    proj [n, *]: q, k, v and the output gate at the columns `cols` = (q, k, v, g); gates [n, 2H] float32; coef
+    [n, 3H] and o [n, H V] float32 scratch; y [n, H V] = o / rms(o per head) * norm_w * sigmoid(g)."""
+    _dev(gates, state, coef, o, norm_w, y, seg_start, seg_len, seg_slot)
+    n = proj.shape[0]
+    assert proj.stride(1) == 1 and gates.dtype == torch.float32 and gates.shape == (n, 2 * H) and state.dtype == torch.float32
+    assert state.shape[1] == mlstm_state_floats(H, D, V) and coef.numel() >= 3 * n * H and o.shape == (n, H * V)
+    assert y.shape == (n, H * V) and y.dtype == proj.dtype and norm_w.dtype == torch.float32 and norm_w.numel() == H * V
+    _check(lib().xr_mlstm(proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), cols[0], cols[1], cols[2], cols[3],
+                          gates.data_ptr(), state.data_ptr(), coef.data_ptr(), o.data_ptr(), norm_w.data_ptr(), y.data_ptr(),
+                          seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), n, n_seg, H, D, V, float(cap), float(eps),
+                          _stream()), "mlstm")
+    _count(3)
+
+
+# ---------------------------------------------------------------------------
+# Routed experts (csrc/moe.cu)
+def route_topk(z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int) -> None:
+    """ids[t], wts[t]: the `top` largest of z[t] (ties: lower index) and the softmax over them alone."""
+    _dev(z, ids, wts)
+    n, E = z.shape
+    assert z.dtype == torch.float32 and ids.dtype == torch.int32 and wts.dtype == torch.float32
+    assert ids.shape == (n, top) and wts.shape == (n, top)
+    _check(lib().xr_route_topk(z.data_ptr(), ids.data_ptr(), wts.data_ptr(), n, E, top, _stream()), "route_topk")
+    _count()
+
+
+def moe_tile_rows() -> int:
+    return int(lib().xr_moe_tile_rows())
+
+
+def moe_max_tiles(pairs: int, E: int) -> int:
+    return pairs // moe_tile_rows() + E + 1
+
+
+def moe_plan(ids: torch.Tensor, row_pair, pair_row, tile_info, plan_counts, E: int) -> None:
+    """Sort the (token, choice) pairs by expert on the device: see k_moe_plan in csrc/moe.cu."""
+    _dev(ids, row_pair, pair_row, tile_info, plan_counts)
+    pairs = ids.numel()
+    assert row_pair.numel() >= pairs and pair_row.numel() >= pairs and tile_info.numel() >= 3 * moe_max_tiles(pairs, E)
+    _check(lib().xr_moe_plan(ids.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(), tile_info.data_ptr(), plan_counts.data_ptr(),
+                             pairs, E, _stream()), "moe_plan")
+    _count()
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_pair, tile_info, plan_counts, pairs: int, top: int,
+             gated: bool, act: int = ACT_NONE, limit: float = 0.0) -> None:
+    """The experts' products over the planned rows.  gated: a = h [n, K], w [E, 2F, K], out [pairs, F] =
+    gate_act(h . w_gate, h . w_up); else a [pairs, K], w [E, N, K], out [pairs, N]."""
+    _dev(a, w, out)
+    E, rows, K = w.shape
+    N = rows // 2 if gated else rows
+    assert a.shape[1] == K and out.shape == (pairs, N)
+    _check(lib().xr_moe_gemm(a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
+                             dtype_code(out.dtype), out.stride(0), row_pair.data_ptr(), tile_info.data_ptr(), plan_counts.data_ptr(),
+                             moe_max_tiles(pairs, E), top, N, K, int(gated), int(act), float(limit), _stream()), "moe_gemm")
+    _count()
+
+
+def moe_combine(d: torch.Tensor, z: torch.Tensor, wts: torch.Tensor, pair_row: torch.Tensor, top: int) -> None:
+    """d[t] += sum_j wts[t, j] * z[pair_row[t * top + j]] (float32)."""
+    _dev(d, z, wts, pair_row)
+    n, width = d.shape
+    assert d.dtype == torch.float32 and z.dtype == torch.float32 and z.shape[1] == width
+    _check(lib().xr_moe_combine(d.data_ptr(), z.data_ptr(), wts.data_ptr(), pair_row.data_ptr(), n, width, top, _stream()), "moe_combine")
     _count()

@@ -2,9 +2,13 @@
 from .base import (Block, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncoding, Rotary, Runtime, StateNeed, kinds, make,
                    register_block, register_feed_forward, register_mixer, register_norm, register_position)
 from .attention import GQAAttention
-from .block import PreNormBlock
+from .block import ParallelBlock, PreNormBlock
 from .embedding import Embedding, Head
 from .feed_forward import GatedFeedForward, MLP, SwiGLU
+from .latent_attention import LatentAttention
 from .linear import Linear
+from .mlstm import MLSTM
+from .moe import RoutedExperts
 from .norm import RMSNorm
 from .position import NoPosition, Rope
+from .stream import StreamJoin

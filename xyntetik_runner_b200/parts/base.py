@@ -57,6 +57,7 @@ class KVNeed:
     kv_heads: int
     head_dim: int
     window: Optional[int] = None    # None: all keys; w: the last w keys
+    planes: int = 2                 # arrays per token: 2 (keys and values), 1 for a mixer that caches one row per token
 
 
 @dataclass(frozen=True)

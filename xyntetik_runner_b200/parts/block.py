@@ -3,6 +3,8 @@
 inside the last product of the mixer and of the feed-forward."""
 from __future__ import annotations
 
+import torch
+
 from .base import Block, FeedForward, Mixer, Norm, register_block
 
 
@@ -41,3 +43,47 @@ class PreNormBlock(Block):
 
 
 register_block("prenorm", PreNormBlock)
+
+
+class ParallelBlock(Block):
+    """One norm, and mixer and feed-forward side by side on its output:  h = norm(x);  x += m (mixer(h) + ff(h)).
+    The sublayers add into a float32 stream of their own, which is added to x once, times the multiplier m."""
+
+    def __init__(self, norm: Norm, mixer: Mixer, feed_forward, residual_mult: float = 1.0):
+        self.norm, self.mixer, self.feed_forward, self.mult = norm, mixer, feed_forward, float(residual_mult)
+
+    def parts(self):
+        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts())
+
+    def tensors(self):
+        out = {}
+        for p in self.parts():
+            out.update(p.tensors())
+        return out
+
+    def bind(self, tensors, rt):
+        for p in self.parts():
+            p.bind(tensors, rt)
+
+    def weight_bytes(self):
+        return sum(p.weight_bytes() for p in self.parts())
+
+    def forward(self, ctx, x, lay):
+        from .. import kernels
+        n, width = x.shape
+        h = ctx.buf("block_normed", (n, width), ctx.act_dtype)
+        self.norm.forward(ctx, x, h)
+        d = ctx.buf("block_sum", (n, width), torch.float32)
+        d.zero_()
+        self.mixer.forward(ctx, h, d, lay)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(ctx, h, d)
+        ctx.materialize(d)
+        kernels.scaled_add(x, d, self.mult)
+
+
+register_block("parallel", ParallelBlock)

@@ -16,8 +16,9 @@ from .linear import Linear
 
 class Embedding(Part):
     graph_safe = True
-    def __init__(self, vocab: int, width: int, name: str):
-        self.vocab, self.width, self.name = vocab, width, name
+    def __init__(self, vocab: int, width: int, name: str, scale: float = 1.0):
+        """`scale` multiplies every embedded row (1: none)."""
+        self.vocab, self.width, self.name, self.scale = vocab, width, name, float(scale)
         self.table = None
 
     def tensors(self):
@@ -28,16 +29,18 @@ class Embedding(Part):
 
     def forward(self, ctx, ids: torch.Tensor, x: torch.Tensor) -> None:
         # ids below zero stand for tokens an earlier step left on the device (the step context's `token_feed`)
-        kernels.embed(self.table, ids, x, getattr(ctx, "token_feed", None))
+        kernels.embed(self.table, ids, x, getattr(ctx, "token_feed", None), self.scale)
 
 
 class Head(Part):
     graph_safe = True
     """`tied_to` set: no tensor of its own, multiplies by the embedding table."""
 
-    def __init__(self, vocab: int, width: int, name: str = None, tied_to: Embedding = None):
+    def __init__(self, vocab: int, width: int, name: str = None, tied_to: Embedding = None, softcap: float = None):
+        """`softcap` c: the logits become c tanh(logits / c) (None or 0: as they are)."""
         assert (name is None) != (tied_to is None)
         self.vocab, self.width, self.name, self.tied_to = vocab, width, name, tied_to
+        self.softcap = float(softcap) if softcap else None
         self.linear = None
 
     def tensors(self):
@@ -53,3 +56,5 @@ class Head(Part):
 
     def forward(self, ctx, h: torch.Tensor, logits: torch.Tensor) -> None:
         self.linear.forward(h, logits)
+        if self.softcap is not None:
+            kernels.softcap(logits, self.softcap)

@@ -22,9 +22,12 @@ class GatedFeedForward(FeedForward):
     graph_safe = True
 
     def __init__(self, width: int, inner: int, prefix: str, activation: str = "silu",
-                 gate: str = "gate_proj.weight", up: str = "up_proj.weight", down: str = "down_proj.weight"):
+                 gate: str = "gate_proj.weight", up: str = "up_proj.weight", down: str = "down_proj.weight",
+                 limit: float = 0.0):
+        """`limit`: the clamp of the activation "swish_clamp" (see ``kernels.ACTIVATIONS``); other activations ignore it."""
         self.width, self.inner, self.prefix = width, inner, prefix
         self.act = _act_id(activation)
+        self.limit = float(limit)
         self.names = (prefix + gate, prefix + up, prefix + down)
         self.gate_up = self.down = None
 
@@ -51,7 +54,7 @@ class GatedFeedForward(FeedForward):
         act = ctx.buf("ffn_act", (n, self.inner), ctx.act_dtype)
         # gate and up share the X tile; act(g) * u happens in the product's epilogue where the tensor cores run it
         gu = None if self.gate_up.gated_fused() else ctx.buf("ffn_gate_up", (n, 2 * self.inner), ctx.act_dtype)
-        self.gate_up.forward_gated(h, act, self.act, gu)
+        self.gate_up.forward_gated(h, act, self.act, gu, self.limit)
         ctx.set_pending(x, self.down.forward(act, x, accumulate=True, defer=True))
 
 

@@ -65,15 +65,16 @@ class Linear:
         return self.halves == 2 and self.packed is not None
 
     def forward_gated(self, x: torch.Tensor, out: torch.Tensor, act: int = kernels.ACT_SILU,
-                      scratch: Optional[torch.Tensor] = None) -> None:
-        """out[t][f] = act(x . W_gate[f]) * (x . W_up[f]): in the tensor-core product's epilogue when the matrix is
-        packed for it, else as the product [n, 2F] into `scratch` followed by the activation kernel."""
+                      scratch: Optional[torch.Tensor] = None, limit: float = 0.0) -> None:
+        """out[t][f] = act(x . W_gate[f]) * (x . W_up[f]) (`limit`: the clamp of ACT_SWISH_CLAMP): in the tensor-core
+        product's epilogue when the matrix is packed for it, else as the product [n, 2F] into `scratch` followed by the
+        activation kernel."""
         assert self.halves == 2
         if self.packed is not None:
-            kernels.gemm_tc(x, self.packed, out, None, kernels.EPI_GATED, packed_rows=self.n_out // 2, act=act)
+            kernels.gemm_tc(x, self.packed, out, None, kernels.EPI_GATED, packed_rows=self.n_out // 2, act=act, act_limit=limit)
             counters["tcgen05"] += 1
             return
         assert scratch is not None and scratch.shape == (x.shape[0], self.n_out)
         kernels.gemm_simt(x, self.weight, scratch, None, False)
         counters["simt"] += 1
-        kernels.act_mul(scratch, out, act, gated=True)
+        kernels.act_mul(scratch, out, act, gated=True, limit=limit)

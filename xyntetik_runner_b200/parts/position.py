@@ -59,6 +59,10 @@ class Rope(PositionEncoding):
             inv = (inv / div).astype(np.float32)
         self.inv_freq_host = inv
         self.inv_freq = None
+        # the same frequencies in float64, for kernels that take the angle in float64 (unscaled frequencies only)
+        self.inv_freq64_host = None
+        if scaling is None and half:
+            self.inv_freq64_host = np.power(float(theta), -2.0 * np.arange(half, dtype=np.float64) / float(self.rotary_dim))
 
     def prepare(self, rt):
         self.inv_freq = torch.from_numpy(self.inv_freq_host.copy()).to(rt.device)
