@@ -158,15 +158,39 @@ def test_routed_experts_kernels_against_plain(dtype):
     wts = torch.empty(n, top, device=dev)
     kernels.route_topk(z.to(dev), ids, wts, top)
     pairs = n * top
-    row_pair, pair_row = (torch.empty(pairs, dtype=torch.int32, device=dev) for _ in range(2))
-    tiles = torch.empty(3 * kernels.moe_max_tiles(pairs, E), dtype=torch.int32, device=dev)
-    counts = torch.zeros(4, dtype=torch.int32, device=dev)
-    kernels.moe_plan(ids, row_pair, pair_row, tiles, counts, E)
-    assert sorted(row_pair.tolist()) == list(range(pairs)) and row_pair[pair_row.long()].tolist() == list(range(pairs))
-    y = torch.empty(pairs, F, dtype=dtype, device=dev)
-    kernels.moe_gemm(h.to(dev), wgu.to(dev), y, row_pair, tiles, counts, pairs, top, True, kernels.ACT_SWISH_CLAMP, limit)
-    zz = torch.empty(pairs, W, device=dev)
-    kernels.moe_gemm(y, wd.to(dev), zz, row_pair, tiles, counts, pairs, top, False)
+    align = kernels.moe_tile_rows()
+    max_tiles = kernels.moe_max_tiles(pairs, E, align)
+    rows = max_tiles * align
+    row_src = torch.empty(rows, dtype=torch.int32, device=dev)
+    pair_row = torch.empty(pairs, dtype=torch.int32, device=dev)
+    tiles = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    kernels.moe_plan(ids, row_src, pair_row, tiles, E, align)
+    assert row_src[pair_row.long()].tolist() == list(range(pairs)) and int((row_src >= 0).sum()) == pairs
+    owner = tiles.long().repeat_interleave(align)
+    live = row_src >= 0
+    assert torch.equal(owner[live], ids.reshape(-1).long()[row_src[live].long()])       # every row lies in a tile of its expert
+    assert 5 not in tiles.tolist() or int((ids == 5).sum()) > 0
+    y = torch.zeros(rows, F, dtype=dtype, device=dev)
+    kernels.moe_gemm(h.to(dev), wgu.to(dev), y, row_src, tiles, top, True, kernels.ACT_SWISH_CLAMP, limit)
+    zz = torch.zeros(rows, W, device=dev)
+    kernels.moe_gemm(y, wd.to(dev), zz, row_src, tiles, top, False)
+    if dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0:
+        # the same through the tensor-core product over rows sorted by expert, for every row tile it takes
+        for bn in (16, 32, 64, 128):
+            mt = kernels.moe_max_tiles(pairs, E, bn)
+            rs = torch.empty(mt * bn, dtype=torch.int32, device=dev)
+            pr = torch.empty(pairs, dtype=torch.int32, device=dev)
+            tg = torch.empty(mt, dtype=torch.int32, device=dev)
+            kernels.moe_plan(ids, rs, pr, tg, E, bn)
+            xs = torch.empty(mt * bn, W, dtype=dtype, device=dev)
+            kernels.moe_gather(h.to(dev), xs, rs, tg, top, bn)
+            y2 = torch.zeros(mt * bn, F, dtype=dtype, device=dev)
+            kernels.gemm_tc_grouped(xs, kernels.pack_weight_groups(wgu.to(dev), 2), y2, tg, bn, F, kernels.EPI_GATED, kernels.ACT_SWISH_CLAMP, limit)
+            z2 = torch.zeros(mt * bn, W, device=dev)
+            kernels.gemm_tc_grouped(y2, kernels.pack_weight_groups(wd.to(dev)), z2, tg, bn, W)
+            kernels.tc_check_status(torch.device(dev))
+            a, b2 = z2[pr.long()], zz[pair_row.long()]
+            assert (a - b2).abs().max() < 2e-2 * b2.abs().max(), bn
     d = torch.ones(n, W, device=dev)
     kernels.moe_combine(d, zz, wts, pair_row, top)
     want = torch.ones(n, W, dtype=torch.float64)

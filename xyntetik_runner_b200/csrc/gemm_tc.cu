@@ -167,6 +167,10 @@ struct TcParams {
     int packed;                 // W is stored tile by tile: [row tile][K block][128][64], see xr_gemm_tc
     int w_kblocks;              // packed: K blocks per row tile in the packed array
     int tok_tiles, pair_tiles;  // CTA-pair kernel: token tiles, and tiles in all (token tiles x pairs of row tiles)
+    // Grouped products (xr_gemm_tc_grouped): W holds several matrices of equal shape one after another, and token tile t
+    // multiplies by matrix tile_group[t] (below zero: the tile holds no rows and its CTAs leave at once)
+    const int* tile_group;
+    int group_row_tiles;        // row tiles of one matrix in the packed array
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -287,6 +291,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int nkb = kb1 - kb0;                     // >= 1: splits <= total_kb
 
     xr_pdl_launch();
+    int w_tile0 = blockIdx.y;                      // this CTA's row tile in the packed array
+    if (p.tile_group != nullptr) {
+        // which matrix a token tile meets was decided by a kernel of this step: it is read after the wait, and a
+        // tile without rows ends here, before any barrier or tensor memory exists
+        xr_pdl_wait();
+        const int group = p.tile_group[blockIdx.x];
+        if (group < 0) return;
+        w_tile0 += group * p.group_row_tiles;
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
@@ -309,7 +322,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         mbar_expect_tx(&full[s], W_BYTES + p.bn * TC_BK * 2);
         if (p.packed) {
             // tile (row tile, K block) is 128 consecutive rows of 64 elements: one contiguous 16 KB read
-            tma_load_2d(st, &map_w, 0, (blockIdx.y * p.w_kblocks + kb0 + i) * TC_BM, &full[s]);
+            tma_load_2d(st, &map_w, 0, (w_tile0 * p.w_kblocks + kb0 + i) * TC_BM, &full[s]);
         } else {
             tma_load_2d(st, &map_w, (kb0 + i) * TC_BK, row0, &full[s]);
         }
@@ -840,6 +853,41 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     int blocks = (int)((total + 255) / 256 < (size_t)most ? (total + 255) / 256 : most);
     xr_launch(k_splitk_finish, dim3(blocks), dim3(256), 0, stream, f);
     return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Grouped product: `groups` matrices of equal shape, packed one after another ([group][row tile][K block][128][64]),
+// and rows of X sorted by the matrix they meet, every group's rows starting at a multiple of `bn` (16, 32, 64 or 128):
+// token tile t of X multiplies by matrix tile_group[t] (an int per tile, on the device; below zero: no rows).  n is the
+// number of rows of X and out that the plan may use (a multiple of bn).  Store and gated epilogues; never cut along K.
+// ---------------------------------------------------------------------------------------------
+XR_EXPORT int xr_gemm_tc_grouped(const void* X, const void* W, void* out, int out_dtype, int epilogue, int act, float act_limit,
+                                 int n, int n_out, int K, long long ldx, long long ldo, int bn, const int* tile_group, int groups,
+                                 int* status, cudaStream_t stream) {
+    if (n < 1 || n_out < 1 || K < 8 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || ldo < n_out || groups < 1) return XR_ERR_ARG;
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15) || tile_group == nullptr) return XR_ERR_ARG;
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128) return XR_ERR_ARG;
+    if ((n % bn) != 0) return XR_ERR_ARG;
+    if (epilogue != TC_EPI_STORE && epilogue != TC_EPI_GATED) return XR_ERR_ARG;
+    if (out_dtype != XR_F32 && out_dtype != XR_BF16) return XR_ERR_ARG;
+    const bool gated = epilogue == TC_EPI_GATED;
+    if (act != TC_ACT_NONE && act != TC_ACT_SILU && act != TC_ACT_GELU_TANH && !(act == TC_ACT_SWISH_CLAMP && gated)) return XR_ERR_ARG;
+    const int row_tiles = gated ? (n_out + 63) / 64 : (n_out + TC_BM - 1) / TC_BM;
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int tok_tiles = n / bn;
+    if (row_tiles > 65535) return XR_ERR_ARG;
+    CUtensorMap mw, mx;
+    if (!make_map(&mw, W, (long long)groups * row_tiles * TC_BM * total_kb, TC_BK, TC_BK, TC_BM)) return -3;
+    if (!make_map(&mx, X, n, K, ldx, bn)) return -3;
+    TcParams p{out, nullptr, nullptr, status, ldo, n, n_out, K, 1, epilogue, out_dtype, act, act_limit, gated ? 1 : 0, bn, 1, total_kb,
+               tok_tiles, 0, tile_group, row_tiles};
+    dim3 grid(tok_tiles, row_tiles, 1);
+    switch (bn) {
+        case 16: return launch_tc<16, 4, 3>(mw, mx, p, grid, stream);
+        case 32: return launch_tc<32, 5, 2>(mw, mx, p, grid, stream);
+        case 64: return launch_tc<64, 4, 2>(mw, mx, p, grid, stream);
+        default: return launch_tc<128, 5, 1>(mw, mx, p, grid, stream);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------

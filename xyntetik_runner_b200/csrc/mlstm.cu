@@ -20,7 +20,7 @@
 
 #define ML_VS 32          // value columns per block of the scan
 #define ML_RG 8           // row groups (warps) per block of the scan
-#define ML_CHUNK 16       // tokens whose q, k, v are staged together
+#define ML_CHUNK 8        // tokens whose q, k, v are staged together
 
 __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
@@ -60,7 +60,8 @@ k_mlstm_gates(const T* __restrict__ proj, long long ldp, int q_col, int k_col, c
             nsm[d] = nn;
             part = fmaf(nn, qd, part);
         }
-        const float qn = xr_block_sum(part, scratch);
+        // (a block of one warp needs no barrier: every lane owns its elements of n)
+        const float qn = blockDim.x == 32 ? xr_warp_sum(part) : xr_block_sum(part, scratch);
         m = m_new;
         if (threadIdx.x == 0) {
             float* c = coef + ((size_t)t * H + h) * 3;
@@ -73,7 +74,7 @@ k_mlstm_gates(const T* __restrict__ proj, long long ldp, int q_col, int k_col, c
 
 template <typename T>
 __global__ void __launch_bounds__(ML_VS * ML_RG)
-k_mlstm_scan(const T* __restrict__ proj, long long ldp, int q_col, int k_col, int v_col, const float* __restrict__ coef,
+k_mlstm_scan_wide(const T* __restrict__ proj, long long ldp, int q_col, int k_col, int v_col, const float* __restrict__ coef,
              float* __restrict__ state, float* __restrict__ out, const int* __restrict__ seg_start,
              const int* __restrict__ seg_len, const int* __restrict__ seg_slot, int H, int D, int V) {
     xr_pdl_launch();
@@ -132,6 +133,83 @@ k_mlstm_scan(const T* __restrict__ proj, long long ldp, int q_col, int k_col, in
         for (int d = rg; d < D; d += ML_RG) Sg[(size_t)d * V + v0 + col] = S[d * ML_VS + col];
 }
 
+// The same walk with S in registers, for key sizes up to 256: thread (row group rg, column) keeps rows
+// rg * RPT .. rg * RPT + RPT - 1 of its column (RPT = rows per thread, 8 * RPT >= D; rows beyond D stay zero), and reads
+// the staged k and q of a token as float4 that the whole warp shares.
+template <typename T, int RPT>
+__global__ void __launch_bounds__(ML_VS * ML_RG)
+k_mlstm_scan(const T* __restrict__ proj, long long ldp, int q_col, int k_col, int v_col, const float* __restrict__ coef,
+             float* __restrict__ state, float* __restrict__ out, const int* __restrict__ seg_start,
+             const int* __restrict__ seg_len, const int* __restrict__ seg_slot, int H, int D, int V) {
+    xr_pdl_launch();
+    constexpr int DP = ML_RG * RPT;
+    __shared__ __align__(16) float ks[ML_CHUNK][DP];
+    __shared__ __align__(16) float qsm[ML_CHUNK][DP];
+    __shared__ float vs[ML_CHUNK][ML_VS];
+    __shared__ float red[ML_CHUNK][ML_RG][ML_VS];
+    __shared__ float cf[ML_CHUNK][3];
+    const int col = threadIdx.x & (ML_VS - 1), rg = threadIdx.x / ML_VS;
+    const int v0 = blockIdx.x * ML_VS, h = blockIdx.y, seg = blockIdx.z;
+    const int start = seg_start[seg], len = seg_len[seg], slot = seg_slot[seg];
+    const bool col_ok = v0 + col < V;
+    xr_pdl_wait();
+    float* Sg = state + ((size_t)slot * H + h) * ml_state_head(D, V);
+    float S[RPT];
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+        const int d = rg * RPT + i;
+        S[i] = (col_ok && d < D) ? Sg[(size_t)d * V + v0 + col] : 0.f;
+    }
+    const float qscale = 1.0f / sqrtf((float)D);
+    for (int j0 = 0; j0 < len; j0 += ML_CHUNK) {
+        const int cnt = min(ML_CHUNK, len - j0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < cnt * DP; e += blockDim.x) {
+            const int j = e / DP, d = e % DP;
+            const T* row = proj + (size_t)(start + j0 + j) * ldp;
+            ks[j][d] = d < D ? xr_to_f32<T>(row[k_col + h * D + d]) : 0.f;
+            qsm[j][d] = d < D ? xr_to_f32<T>(row[q_col + h * D + d]) * qscale : 0.f;
+        }
+        for (int e = threadIdx.x; e < cnt * ML_VS; e += blockDim.x) {
+            const int j = e / ML_VS, c = e % ML_VS;
+            vs[j][c] = v0 + c < V ? xr_to_f32<T>(proj[(size_t)(start + j0 + j) * ldp + v_col + h * V + v0 + c]) : 0.f;
+        }
+        for (int e = threadIdx.x; e < cnt * 3; e += blockDim.x) cf[e / 3][e % 3] = coef[((size_t)(start + j0 + e / 3) * H + h) * 3 + e % 3];
+        __syncthreads();
+        for (int j = 0; j < cnt; j++) {
+            const float f = cf[j][0], iv = cf[j][1] * vs[j][col];
+            const float4* k4 = reinterpret_cast<const float4*>(&ks[j][rg * RPT]);
+            const float4* q4 = reinterpret_cast<const float4*>(&qsm[j][rg * RPT]);
+            float num = 0.f;
+#pragma unroll
+            for (int i = 0; i < RPT / 4; i++) {
+                const float4 kk = k4[i], qq = q4[i];
+                S[4 * i] = fmaf(f, S[4 * i], iv * kk.x);         num = fmaf(S[4 * i], qq.x, num);
+                S[4 * i + 1] = fmaf(f, S[4 * i + 1], iv * kk.y); num = fmaf(S[4 * i + 1], qq.y, num);
+                S[4 * i + 2] = fmaf(f, S[4 * i + 2], iv * kk.z); num = fmaf(S[4 * i + 2], qq.z, num);
+                S[4 * i + 3] = fmaf(f, S[4 * i + 3], iv * kk.w); num = fmaf(S[4 * i + 3], qq.w, num);
+            }
+            red[j][rg][col] = num;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < cnt * ML_VS; e += blockDim.x) {
+            const int j = e / ML_VS, c = e % ML_VS;
+            if (v0 + c >= V) continue;
+            float num = 0.f;
+#pragma unroll
+            for (int r = 0; r < ML_RG; r++) num += red[j][r][c];
+            out[(size_t)(start + j0 + j) * H * V + (size_t)h * V + v0 + c] = num / cf[j][2];
+        }
+    }
+    if (col_ok) {
+#pragma unroll
+        for (int i = 0; i < RPT; i++) {
+            const int d = rg * RPT + i;
+            if (d < D) Sg[(size_t)d * V + v0 + col] = S[i];
+        }
+    }
+}
+
 // o [n][H][V] float32 -> y [n][H * V] (activation dtype): o / rms(o over the head) * w * sigmoid(g); one warp per (token, head)
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -170,15 +248,24 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
     dim3 gg(H, n_seg), gs((V + ML_VS - 1) / ML_VS, H, n_seg);
     const long long warps = (long long)n * H;
     const unsigned gb = (unsigned)((warps + 3) / 4);
+#define SCAN_ARGS(T) gs, dim3(ML_VS * ML_RG), 0, stream, (const T*)proj, ldp, q_col, k_col, v_col, (const float*)coef, state, o, seg_start, seg_len, seg_slot, H, D, V
+#define SCAN(T)                                                                                                                       \
+    do {                                                                                                                              \
+        if (D <= 32) xr_launch((k_mlstm_scan<T, 4>), SCAN_ARGS(T));                                                                   \
+        else if (D <= 64) xr_launch((k_mlstm_scan<T, 8>), SCAN_ARGS(T));                                                              \
+        else if (D <= 128) xr_launch((k_mlstm_scan<T, 16>), SCAN_ARGS(T));                                                            \
+        else if (D <= 256) xr_launch((k_mlstm_scan<T, 32>), SCAN_ARGS(T));                                                            \
+        else xr_launch((k_mlstm_scan_wide<T>), gs, dim3(ML_VS * ML_RG), smem_s, stream, (const T*)proj, ldp, q_col, k_col, v_col,      \
+                       (const float*)coef, state, o, seg_start, seg_len, seg_slot, H, D, V);                                          \
+    } while (0)
 #define ML(T)                                                                                                                         \
     do {                                                                                                                              \
-        if (smem_s > 48 * 1024 &&                                                                                                     \
-            cudaFuncSetAttribute(k_mlstm_scan<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s) != cudaSuccess)           \
+        if (D > 256 && smem_s > 48 * 1024 &&                                                                                                     \
+            cudaFuncSetAttribute(k_mlstm_scan_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s) != cudaSuccess)      \
             return XR_ERR_LAUNCH;                                                                                                     \
-        xr_launch((k_mlstm_gates<T>), gg, dim3(256), smem_g, stream, (const T*)proj, ldp, q_col, k_col, gates, state, coef, seg_start, \
+        xr_launch((k_mlstm_gates<T>), gg, dim3(D <= 512 ? 32 : 256), smem_g, stream, (const T*)proj, ldp, q_col, k_col, gates, state, coef, seg_start, \
                   seg_len, seg_slot, H, D, V, cap);                                                                                   \
-        xr_launch((k_mlstm_scan<T>), gs, dim3(ML_VS * ML_RG), smem_s, stream, (const T*)proj, ldp, q_col, k_col, v_col,                \
-                  (const float*)coef, state, o, seg_start, seg_len, seg_slot, H, D, V);                                               \
+        SCAN(T);                                                                                                                      \
         xr_launch((k_mlstm_out<T>), dim3(gb), dim3(128), 0, stream, (const float*)o, (const T*)proj, ldp, g_col, norm_w, (T*)y, n, H, \
                   V, eps);                                                                                                            \
     } while (0)
@@ -186,5 +273,7 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
     else if (dtype == XR_BF16) ML(__nv_bfloat16);
     else return XR_ERR_ARG;
 #undef ML
+#undef SCAN
+#undef SCAN_ARGS
     return xr_launch_status();
 }

@@ -56,66 +56,97 @@ XR_EXPORT int xr_route_topk(const float* z, int* ids, float* wts, int n, int E, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Plan, one block: rows = the n * top pairs sorted by expert.
-//   row_pair [pairs]: the pair (t * top + j) that row r computes;  pair_row [pairs]: the inverse;
-//   tiles of MOE_TM rows that never span two experts: tile_info [max_tiles][3] = (expert, first row, rows), and
-//   plan_counts[0] = number of tiles.  max_tiles = pairs / MOE_TM + E + 1 always suffices.
+// Plan, one block: rows = the n * top pairs sorted by expert, every expert's rows starting at a multiple of `align`
+// (the row tile of the kernel that multiplies them), so that a tile of `align` rows meets one expert.
+//   row_src [max_rows]: the pair (t * top + j) that row r computes, -1 for a row of padding;
+//   pair_row [pairs]: the row of every pair;  tile_group [max_rows / align]: the tile's expert, -1 for a tile without rows.
+//   max_rows = (pairs / align + E + 1) * align always suffices.
 // Which row a pair gets among its expert's rows depends on the order in which threads arrive; a row's result does not.
 // ---------------------------------------------------------------------------------------------
-#define MOE_TM 64
 #define MOE_MAX_E 1024
 
 __global__ void __launch_bounds__(1024)
-k_moe_plan(const int* __restrict__ ids, int* __restrict__ row_pair, int* __restrict__ pair_row, int* __restrict__ tile_info,
-           int* __restrict__ plan_counts, int pairs, int E) {
+k_moe_plan(const int* __restrict__ ids, int* __restrict__ row_src, int* __restrict__ pair_row, int* __restrict__ tile_group,
+           int pairs, int E, int align, int max_tiles) {
     xr_pdl_launch();
-    __shared__ int count[MOE_MAX_E], first[MOE_MAX_E], cursor[MOE_MAX_E], tile0[MOE_MAX_E + 1];
+    __shared__ int count[MOE_MAX_E], cursor[MOE_MAX_E], tile0[MOE_MAX_E + 1];
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     xr_pdl_wait();
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[ids[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
-        int at = 0, tiles = 0;
+        int tiles = 0;
         for (int e = 0; e < E; e++) {
-            first[e] = at; cursor[e] = at; tile0[e] = tiles;
-            at += count[e];
-            tiles += (count[e] + MOE_TM - 1) / MOE_TM;
+            tile0[e] = tiles; cursor[e] = tiles * align;
+            tiles += (count[e] + align - 1) / align;
         }
         tile0[E] = tiles;
-        plan_counts[0] = tiles;
     }
     __syncthreads();
+    const int used = tile0[E];
+    for (int r = threadIdx.x; r < max_tiles * align; r += blockDim.x) row_src[r] = -1;
+    for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_group[t] = -1;
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
+        for (int t = tile0[e]; t < tile0[e + 1]; t++) tile_group[t] = e;
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int r = atomicAdd(&cursor[ids[p]], 1);
-        row_pair[r] = p;
+        row_src[r] = p;
         pair_row[p] = r;
     }
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        const int nt = tile0[e + 1] - tile0[e];
-        for (int i = 0; i < nt; i++) {
-            int* ti = tile_info + (size_t)(tile0[e] + i) * 3;
-            ti[0] = e; ti[1] = first[e] + i * MOE_TM; ti[2] = min(MOE_TM, count[e] - i * MOE_TM);
-        }
-    }
+    (void)used;
 }
 
-XR_EXPORT int xr_moe_plan(const int* ids, int* row_pair, int* pair_row, int* tile_info, int* plan_counts, int pairs, int E,
+XR_EXPORT int xr_moe_plan(const int* ids, int* row_src, int* pair_row, int* tile_group, int pairs, int E, int align, int max_tiles,
                           cudaStream_t stream) {
-    if (pairs < 1 || E < 1 || E > MOE_MAX_E) return XR_ERR_ARG;
-    xr_launch(k_moe_plan, dim3(1), dim3(1024), 0, stream, ids, row_pair, pair_row, tile_info, plan_counts, pairs, E);
+    if (pairs < 1 || E < 1 || E > MOE_MAX_E || align < 1 || max_tiles < pairs / align + E) return XR_ERR_ARG;
+    xr_launch(k_moe_plan, dim3(1), dim3(1024), 0, stream, ids, row_src, pair_row, tile_group, pairs, E, align, max_tiles);
     return xr_launch_status();
 }
 
-XR_EXPORT int xr_moe_tile_rows() { return MOE_TM; }
+// ---------------------------------------------------------------------------------------------
+// out[r] = h[row_src[r] / top] for the rows of tiles that hold any, zeros for rows of padding: the first product's
+// input in the order of the plan, for the tensor-core product (which reads its rows through a tensor map).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+k_moe_gather(const T* __restrict__ h, long long ldh, T* __restrict__ out, const int* __restrict__ row_src,
+             const int* __restrict__ tile_group, int top, int width, int align) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const int r = blockIdx.x;
+    if (tile_group[r / align] < 0) return;
+    const int src = row_src[r];
+    T* o = out + (size_t)r * width;
+    if (src < 0) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = xr_from_f32<T>(0.f);
+        return;
+    }
+    const T* a = h + (size_t)(src / top) * ldh;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = a[i];
+}
+
+XR_EXPORT int xr_moe_gather(const void* h, int dtype, long long ldh, void* out, const int* row_src, const int* tile_group, int top,
+                            int width, int align, int max_rows, cudaStream_t stream) {
+    if (max_rows < 1 || width < 1 || top < 1 || align < 1) return XR_ERR_ARG;
+    if (dtype == XR_F32) xr_launch((k_moe_gather<float>), dim3(max_rows), dim3(256), 0, stream, (const float*)h, ldh, (float*)out, row_src, tile_group, top, width, align);
+    else if (dtype == XR_BF16) xr_launch((k_moe_gather<__nv_bfloat16>), dim3(max_rows), dim3(256), 0, stream, (const __nv_bfloat16*)h, ldh, (__nv_bfloat16*)out, row_src, tile_group, top, width, align);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
 
 // ---------------------------------------------------------------------------------------------
-// The experts' products over the planned tiles, float32 FMA, k in ascending order for every result.
-//  first product (gated = 1): rows gather their token's h (row_pair[r] / top); W = [E][2F][K] (an expert's gate rows,
-//    then its up rows); out Y [pairs][F] in the activation dtype = gate_act(h . w_gate_f, h . w_up_f).
-//  second product (gated = 0): rows read Y [pairs][K = F]; W = [E][N][K]; out Z [pairs][N] float32.
+// The experts' products over the planned tiles (align = 64 rows), float32 FMA, k in ascending order for every result:
+// the products of the true 32-bit path and of sizes the tensor-core product does not take.
+//  first product (gated = 1): rows gather their token's h (row_src[r] / top); W = [E][2F][K] (an expert's gate rows,
+//    then its up rows); out Y [rows][F] in the activation dtype = gate_act(h . w_gate_f, h . w_up_f).
+//  second product (gated = 0): rows read Y [rows][K = F]; W = [E][N][K]; out Z [rows][N] float32.
 // Tile: 64 rows x 64 columns (gated: 32 features, gate and up side by side), 256 threads with 4 x 4 results each.
 // ---------------------------------------------------------------------------------------------
+#define MOE_TM 64
+XR_EXPORT int xr_moe_tile_rows() { return MOE_TM; }
+
 __device__ __forceinline__ float moe_gate(int act, float limit, float g, float u) {
     if (act == 3) {                  // g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit)
         g = fminf(g, limit);
@@ -130,20 +161,20 @@ __device__ __forceinline__ float moe_gate(int act, float limit, float g, float u
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 k_moe_gemm(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, TO* __restrict__ out, long long ldo,
-           const int* __restrict__ row_pair, const int* __restrict__ tile_info, const int* __restrict__ plan_counts,
-           int top, int N, int K, int gated, int act, float limit) {
+           const int* __restrict__ row_src, const int* __restrict__ tile_group, int top, int N, int K, int gated, int act, float limit) {
     xr_pdl_launch();
     __shared__ float As[16][64 + 1], Ws[16][64 + 1];
     __shared__ int src_row[64];
     xr_pdl_wait();
-    if ((int)blockIdx.x >= plan_counts[0]) return;
-    const int e = tile_info[blockIdx.x * 3], r0 = tile_info[blockIdx.x * 3 + 1], rows = tile_info[blockIdx.x * 3 + 2];
+    const int e = tile_group[blockIdx.x];
+    if (e < 0) return;
+    const int r0 = blockIdx.x * MOE_TM;
     const int cols = gated ? 32 : 64;                 // output columns (features) per tile
     const int c0 = blockIdx.y * cols;
     const TW* We = W + (size_t)e * (gated ? 2 : 1) * N * K;
     if (threadIdx.x < 64) {
-        int r = threadIdx.x;
-        src_row[r] = r < rows ? (gated ? row_pair[r0 + r] / top : r0 + r) : -1;
+        const int r = threadIdx.x, s = row_src[r0 + r];
+        src_row[r] = s < 0 ? -1 : (gated ? s / top : r0 + r);
     }
     __syncthreads();
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -176,7 +207,7 @@ k_moe_gemm(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, TO
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int r = ty + 16 * i;
-        if (r >= rows) continue;
+        if (src_row[r] < 0) continue;
         TO* orow = out + (size_t)(r0 + r) * ldo;
         if (gated) {
             // this thread's columns tx, tx + 16 are gate sums, tx + 32, tx + 48 the up sums of the same two features
@@ -195,9 +226,9 @@ k_moe_gemm(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, TO
     }
 }
 
-// dtype: of the activations (A of the first product, Y); w_dtype: of the experts' matrices.
+// a_dtype: of A; w_dtype: of the experts' matrices; max_tiles: tiles of 64 rows the plan may use.
 XR_EXPORT int xr_moe_gemm(const void* A, int a_dtype, long long lda, const void* W, int w_dtype, void* out, int out_dtype,
-                          long long ldo, const int* row_pair, const int* tile_info, const int* plan_counts, int max_tiles,
+                          long long ldo, const int* row_src, const int* tile_group, int max_tiles,
                           int top, int N, int K, int gated, int act, float limit, cudaStream_t stream) {
     if (max_tiles < 1 || N < 1 || K < 1 || top < 1 || act < 0 || act > 3) return XR_ERR_ARG;
     const int cols = gated ? 32 : 64;
@@ -205,7 +236,7 @@ XR_EXPORT int xr_moe_gemm(const void* A, int a_dtype, long long lda, const void*
     if (grid.y > 65535) return XR_ERR_ARG;
     typedef __nv_bfloat16 bf;
 #define MG(TA, TW, TO) xr_launch((k_moe_gemm<TA, TW, TO>), grid, dim3(256), 0, stream, (const TA*)A, lda, (const TW*)W, (TO*)out, ldo, \
-                                 row_pair, tile_info, plan_counts, top, N, K, gated, act, limit)
+                                 row_src, tile_group, top, N, K, gated, act, limit)
     const int key = a_dtype * 4 + w_dtype * 2 + out_dtype;
     switch (key) {
         case XR_BF16 * 4 + XR_BF16 * 2 + XR_BF16: MG(bf, bf, bf); break;

@@ -77,9 +77,11 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_latent_attention": [_vp, _vp, _i, _ll, _i, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_mlstm": [_vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
         "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
-        "xr_moe_plan": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
+        "xr_moe_plan": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+        "xr_moe_gather": [_vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+        "xr_gemm_tc_grouped": [_vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _ll, _ll, _i, _vp, _i, _vp, _vp],
         "xr_moe_tile_rows": [],
-        "xr_moe_gemm": [_vp, _i, _ll, _vp, _i, _vp, _i, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_moe_gemm": [_vp, _i, _ll, _vp, _i, _vp, _i, _ll, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
     }
     for name, args in sig.items():
@@ -715,34 +717,71 @@ def route_topk(z: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, top: int) 
 
 
 def moe_tile_rows() -> int:
+    """Rows per tile of the FMA kernel of the experts' products (the alignment its plan needs)."""
     return int(lib().xr_moe_tile_rows())
 
 
-def moe_max_tiles(pairs: int, E: int) -> int:
-    return pairs // moe_tile_rows() + E + 1
+def moe_max_tiles(pairs: int, E: int, align: int) -> int:
+    """Tiles of `align` rows that a plan over `pairs` rows and E experts can need at most."""
+    return pairs // align + E + 1
 
 
-def moe_plan(ids: torch.Tensor, row_pair, pair_row, tile_info, plan_counts, E: int) -> None:
-    """Sort the (token, choice) pairs by expert on the device: see k_moe_plan in csrc/moe.cu."""
-    _dev(ids, row_pair, pair_row, tile_info, plan_counts)
+def moe_plan(ids: torch.Tensor, row_src, pair_row, tile_group, E: int, align: int) -> None:
+    """Sort the (token, choice) pairs by expert on the device, every expert's rows starting at a multiple of `align`:
+    row_src [max_tiles * align] (pair of a row, -1: padding), pair_row [pairs], tile_group [max_tiles] (expert of a
+    tile, -1: no rows); see k_moe_plan in csrc/moe.cu."""
+    _dev(ids, row_src, pair_row, tile_group)
     pairs = ids.numel()
-    assert row_pair.numel() >= pairs and pair_row.numel() >= pairs and tile_info.numel() >= 3 * moe_max_tiles(pairs, E)
-    _check(lib().xr_moe_plan(ids.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(), tile_info.data_ptr(), plan_counts.data_ptr(),
-                             pairs, E, _stream()), "moe_plan")
+    max_tiles = moe_max_tiles(pairs, E, align)
+    assert row_src.numel() >= max_tiles * align and pair_row.numel() >= pairs and tile_group.numel() >= max_tiles
+    _check(lib().xr_moe_plan(ids.data_ptr(), row_src.data_ptr(), pair_row.data_ptr(), tile_group.data_ptr(), pairs, E, align,
+                             max_tiles, _stream()), "moe_plan")
     _count()
 
 
-def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_pair, tile_info, plan_counts, pairs: int, top: int,
+def moe_gather(h: torch.Tensor, out: torch.Tensor, row_src, tile_group, top: int, align: int) -> None:
+    """out[r] = h[row_src[r] // top] for the rows of the plan's tiles (zeros for rows of padding)."""
+    _dev(out, row_src, tile_group)
+    assert h.stride(1) == 1 and out.shape[1] == h.shape[1] and out.dtype == h.dtype and out.shape[0] % align == 0
+    _check(lib().xr_moe_gather(h.data_ptr(), dtype_code(h.dtype), h.stride(0), out.data_ptr(), row_src.data_ptr(),
+                               tile_group.data_ptr(), top, h.shape[1], align, out.shape[0], _stream()), "moe_gather")
+    _count()
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_src, tile_group, top: int,
              gated: bool, act: int = ACT_NONE, limit: float = 0.0) -> None:
-    """The experts' products over the planned rows.  gated: a = h [n, K], w [E, 2F, K], out [pairs, F] =
-    gate_act(h . w_gate, h . w_up); else a [pairs, K], w [E, N, K], out [pairs, N]."""
+    """The experts' products over the planned rows (a plan with align = moe_tile_rows()), float32 FMA.  gated:
+    a = h [n, K], w [E, 2F, K], out [rows, F] = gate_act(h . w_gate, h . w_up); else a [rows, K], w [E, N, K], out [rows, N]."""
     _dev(a, w, out)
     E, rows, K = w.shape
     N = rows // 2 if gated else rows
-    assert a.shape[1] == K and out.shape == (pairs, N)
+    assert a.shape[1] == K and out.shape[1] == N and out.shape[0] % moe_tile_rows() == 0
     _check(lib().xr_moe_gemm(a.data_ptr(), dtype_code(a.dtype), a.stride(0), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
-                             dtype_code(out.dtype), out.stride(0), row_pair.data_ptr(), tile_info.data_ptr(), plan_counts.data_ptr(),
-                             moe_max_tiles(pairs, E), top, N, K, int(gated), int(act), float(limit), _stream()), "moe_gemm")
+                             dtype_code(out.dtype), out.stride(0), row_src.data_ptr(), tile_group.data_ptr(),
+                             out.shape[0] // moe_tile_rows(), top, N, K, int(gated), int(act), float(limit), _stream()), "moe_gemm")
+    _count()
+
+
+def pack_weight_groups(w: torch.Tensor, halves: int = 1) -> torch.Tensor:
+    """``pack_weight`` of every matrix of w [groups, rows, K], one after another: [groups, row tiles, K blocks, 128, 64]."""
+    return torch.stack([pack_weight(w[g], halves) for g in range(w.shape[0])]).contiguous()
+
+
+def gemm_tc_grouped(x: torch.Tensor, w_packed: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, bn: int, n_out: int,
+                    epilogue: int = EPI_STORE, act: int = ACT_NONE, act_limit: float = 0.0) -> None:
+    """bfloat16 product on tcgen05 of rows sorted by group: tile t of `bn` rows of x multiplies by matrix
+    tile_group[t] of w_packed (from ``pack_weight_groups``); tiles with tile_group below zero are skipped.
+    EPI_STORE: out[r] = x[r] . w^T; EPI_GATED (halves = 2 packing): out[r][f] = gate_act(x . w_gate[f], x . w_up[f])."""
+    _dev(x, w_packed, out, tile_group)
+    n, k = x.shape
+    assert x.dtype == torch.bfloat16 and w_packed.dtype == torch.bfloat16 and w_packed.dim() == 5 and n % bn == 0
+    tiles = -(-n_out // GATED_FEATURES) if epilogue == EPI_GATED else -(-n_out // TILE_ROWS)
+    assert w_packed.shape[1] == tiles and w_packed.shape[2] == -(-k // TILE_K) and out.shape == (n, n_out)
+    assert tile_group.dtype == torch.int32 and tile_group.numel() >= n // bn
+    ws = workspace(x.device)
+    _check(lib().xr_gemm_tc_grouped(x.data_ptr(), w_packed.data_ptr(), out.data_ptr(), dtype_code(out.dtype), epilogue, int(act),
+                                    float(act_limit), n, n_out, k, x.stride(0), out.stride(0), bn, tile_group.data_ptr(),
+                                    w_packed.shape[0], ws.status_ptr, _stream()), "gemm_tc_grouped")
     _count()
 
 

@@ -1,0 +1,222 @@
+"""Prefill and decode throughput of a Turudra model beside a dense Llama of equal size, with the time of every kernel
+family inside the steps (``bench.py --designs``).
+
+Sizes resemble real layers; weights are random.  Both models run through the same engine: one prompt of `tokens` tokens
+in one step (prefill), and decode steps of `batch` requests that hold `context` tokens each (``Engine.adopt``: the cache
+holds whatever the pool holds; the recurrent states start at zero).  Step times are CUDA-event times after warm-up; the
+weights of either model exceed the L2 cache, so every step reads them from memory.
+
+Per kernel family, the time inside one step launched kernel by kernel (an event before and after every launch; gaps
+between launches count to the family that follows, so small kernels read high), the FLOPs and bytes the family must
+move, and the larger of FLOPs / time / measured product peak and bytes / time / measured copy bandwidth: the fraction
+of its roofline.
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List
+
+import torch
+
+from . import kernels, measure
+from .config.llama import LlamaConfig
+from .config.turudra import TurudraConfig
+from .engine.engine import EngineParams, StepEntry, random_engine
+
+SIZES = {
+    # name: (width, latent attention, mlstm, experts, top, expert ff, shared ff, vocab)
+    "w1024": (1024, dict(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256), dict(heads=4, dim=128, vdim=256), 16, 2, 512, 1024, 32000),
+    "w2048": (2048, dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512), dict(heads=8, dim=128, vdim=256), 64, 6, 1408, 2816, 32000),
+}
+
+
+def turudra_config(size: str) -> TurudraConfig:
+    W, la, ml, E, top, ff, sff, vocab = SIZES[size]
+    mlp = {"kind": "moe", "router": {"experts": E, "top": top}, "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": sff, "limit": 7.0}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": dict(la, scale=(la["dim"] + la["rot_dim"]) ** -0.5, rot={"base": 10000.0, "dims": la["rot_dim"]})}
+    mlstm = {"type": "mlstm", "mlp": mlp, "mixer": dict(ml, gate_cap=15.0)}
+    return TurudraConfig.from_dict({"architecture": "Turudra", "vocab": vocab, "width": W, "embedding": {"scale": 1.0},
+                                    "residual_mult": 1.0, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+                                    "layers": [mlstm, latent, mlstm, latent], "loop": {"start": 1, "stop": 3, "times": 2}})
+
+
+def llama_config(size: str, layers: int, positions: int) -> LlamaConfig:
+    """A dense decoder of the same width and number of layer runs whose feed-forward is as wide as the experts a token uses."""
+    W, la, ml, E, top, ff, sff, vocab = SIZES[size]
+    return LlamaConfig.from_dict({"architectures": ["LlamaForCausalLM"], "hidden_size": W, "num_hidden_layers": layers,
+                                  "num_attention_heads": W // 128, "num_key_value_heads": max(1, W // 512), "head_dim": 128,
+                                  "intermediate_size": top * ff + sff, "vocab_size": vocab, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+                                  "max_position_embeddings": positions, "torch_dtype": "bfloat16"})
+
+
+FAMILIES = {
+    "gemm_tc": "products (tcgen05)", "gemm_tc_deferred": "products (tcgen05)", "gemm_simt": "products (FMA)",
+    "finish_plain": "products (tcgen05)", "finish_add_rmsnorm": "norms", "rmsnorm": "norms", "finish_rope_store": "rotation + cache store",
+    "rope_store": "rotation + cache store", "attention_tc": "attention", "attention_mma": "attention", "attention_simt": "attention",
+    "latent_prep": "rotation + cache store", "head_matmul": "latent attention: per-head products", "latent_attention": "latent attention: scores and sums",
+    "mlstm": "mlstm recurrence", "route_topk": "routing", "moe_plan": "routing", "moe_gemm": "experts' products", "moe_combine": "experts' sum",
+    "scaled_add": "stream kernels", "concat_cast": "stream kernels", "softcap": "stream kernels", "embed": "stream kernels", "act_mul": "stream kernels",
+}
+
+
+class _Timed:
+    """Events around every launch of the functions in FAMILIES while a step runs."""
+
+    def __init__(self):
+        self.marks: List[tuple] = []
+        self._orig = {}
+
+    def __enter__(self):
+        for name in FAMILIES:
+            fn = getattr(kernels, name)
+            self._orig[name] = fn
+
+            def wrapped(*a, _fn=fn, _name=name, **k):
+                r = _fn(*a, **k)
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                self.marks.append((_name, e))
+                return r
+            setattr(kernels, name, wrapped)
+        self.start = torch.cuda.Event(enable_timing=True)
+        self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        for name, fn in self._orig.items():
+            setattr(kernels, name, fn)
+
+    def by_family(self) -> Dict[str, float]:
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        prev = self.start
+        for name, e in self.marks:
+            out[FAMILIES[name]] = out.get(FAMILIES[name], 0.0) + prev.elapsed_time(e) * 1e3
+            prev = e
+        return out
+
+
+def _work(cfg, tokens: int, keys_per_token: float, decode: bool) -> Dict[str, tuple]:
+    """(FLOPs, bytes) that each Turudra-specific family must move in one step of `tokens` tokens."""
+    out = {}
+    runs = cfg.layer_runs()
+    fl_e = by_e = fl_a = by_a = fl_h = by_m = fl_m = 0.0
+    for i, _ in runs:
+        lay = cfg.layers[i]
+        if lay.mlp is not None:
+            f = lay.mlp
+            fl_e += 2.0 * tokens * f.top * 3 * f.expert.ff * cfg.width
+            used = min(f.experts, tokens * f.top)
+            by_e += used * 3 * f.expert.ff * cfg.width * 2
+        m = lay.mixer
+        if m.kind == "latent_attention":
+            fl_a += 2.0 * tokens * m.heads * keys_per_token * (2 * m.kv_rank + m.rot_dim)
+            by_a += (tokens if decode else 1) * keys_per_token * (m.kv_rank + m.rot_dim) * 2
+            fl_h += 2.0 * tokens * m.heads * m.kv_rank * (m.dim + m.vdim)
+        else:
+            by_m += (tokens if decode else 1) * 2 * m.heads * m.dim * m.vdim * 4
+            fl_m += 4.0 * tokens * m.heads * m.dim * m.vdim
+    out["experts' products"] = (fl_e, by_e)
+    out["latent attention: scores and sums"] = (fl_a, by_a)
+    out["latent attention: per-head products"] = (fl_h, 0.0)
+    out["mlstm recurrence"] = (fl_m, by_m)
+    return out
+
+
+def _llama_work(cfg, tokens, keys_per_token, decode):
+    L, W = cfg.num_hidden_layers, cfg.hidden_size
+    fl_a = 4.0 * tokens * cfg.num_attention_heads * keys_per_token * cfg.head_dim * L
+    by_a = (tokens if decode else 1) * keys_per_token * 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * L
+    per_layer = W * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * W + 3 * W * cfg.intermediate_size
+    fl_p = 2.0 * tokens * (per_layer * L + cfg.vocab_size * W * (1 if decode else 1.0 / tokens))
+    by_p = 2.0 * (per_layer * L + cfg.vocab_size * W)
+    return {"attention": (fl_a, by_a), "products (tcgen05)": (fl_p, by_p)}
+
+
+def _measure(eng, cfg, work_fn, tokens: int, batch: int, context: int, steps: int, warmup: int, pk) -> dict:
+    vocab = eng.plan.vocab_size
+    gen = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
+
+    def prefill_once(timed=None):
+        lg = eng.step([StepEntry("p", prompt, [tokens - 1])])
+        eng.end("p")
+        return lg
+    for _ in range(max(2, warmup // 2)):
+        prefill_once()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        prefill_once()
+    e1.record()
+    torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1) / reps
+    with _Timed() as t:
+        prefill_once()
+    prefill_fam = t.by_family()
+    # decode
+    ids = [f"d{i}" for i in range(batch)]
+    for r in ids:
+        eng.adopt(r, context)
+    toks = torch.randint(0, vocab, (batch,), generator=gen).tolist()
+
+    def decode_once():
+        return eng.step([StepEntry(r, [toks[i]], [0]) for i, r in enumerate(ids)])
+    for _ in range(max(3, warmup)):
+        decode_once()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        decode_once()
+    e1.record()
+    torch.cuda.synchronize()
+    decode_ms = e0.elapsed_time(e1) / steps
+    graphs, eng._graph_ok = eng._graph_ok, False
+    decode_once()
+    with _Timed() as t:
+        decode_once()
+    decode_fam = t.by_family()
+    eng._graph_ok = graphs
+    for r in ids:
+        eng.end(r)
+    eng.check_status()
+
+    def table(fam, work):
+        rows = []
+        for name, us in sorted(fam.items(), key=lambda kv: -kv[1]):
+            row = {"kernels": name, "us": round(us, 1)}
+            if name in work and us > 0:
+                fl, by = work[name]
+                row["tflops"] = round(fl / us / 1e6, 2)
+                row["gbs"] = round(by / us / 1e3, 1)
+                row["frac"] = round(max(fl / us / 1e6 / pk["bf16_tflops"], by / us / 1e3 / pk["hbm_gbs"]), 4)
+            rows.append(row)
+        return rows
+    return {"prefill": {"tokens": tokens, "ms": round(prefill_ms, 3), "tok_s": round(tokens / prefill_ms * 1e3),
+                        "kernels": table(prefill_fam, work_fn(cfg, tokens, (tokens + 1) / 2.0, False))},
+            "decode": {"batch": batch, "context": context, "ms": round(decode_ms, 4), "tok_s": round(batch / decode_ms * 1e3),
+                       "kernels": table(decode_fam, work_fn(cfg, batch, context + steps / 2.0, True))},
+            "weight_bytes_per_step": eng.weight_bytes_per_step()}
+
+
+def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, steps: int = 32, warmup: int = 4, root=None) -> dict:
+    pk = measure.peaks(root)
+    out = {"size": size, "peaks": pk["source"], "dtype": "bf16", "data": "synthetic: random weights, random tokens"}
+    tcfg = turudra_config(size)
+    pool = batch * (context + 64 * (2 + (steps + warmup + 8) // 64)) + tokens + 64
+    ep = lambda: EngineParams(dtype="bfloat16", max_tokens=pool, page_size=64, max_requests=batch + 1,
+                              max_request_tokens=max(tokens, context + steps + warmup + 72), max_step_tokens=tokens)
+    for name, cfg, work in (("turudra", tcfg, _work), ("llama", llama_config(size, len(tcfg.layer_runs()), context + tokens), _llama_work)):
+        t0 = time.perf_counter()
+        eng = random_engine(cfg, 5, ep())
+        for kv in eng.kv:
+            kv.normal_(0.0, 1.0)
+        torch.cuda.synchronize()
+        out[name] = _measure(eng, cfg, work, tokens, batch, context, steps, warmup, pk)
+        out[name]["load_s"] = round(time.perf_counter() - t0, 1)
+        del eng
+        torch.cuda.empty_cache()
+    return out

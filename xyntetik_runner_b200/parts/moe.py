@@ -17,6 +17,7 @@ from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import FeedForward, register_feed_forward
 from .feed_forward import GatedFeedForward, _act_id
+from . import linear_tc
 from .linear import Linear
 
 
@@ -33,6 +34,7 @@ class RoutedExperts(FeedForward):
         self.router_name = prefix + router
         self.expert_names = [tuple(prefix + expert.format(e) + s for s in (gate, up, down)) for e in range(experts)]
         self.router = self.w_gate_up = self.w_down = None
+        self.tensor_cores, self._nbytes = False, 0
 
     def tensors(self):
         t = {self.router_name: TensorSpec((self.E, self.width))}
@@ -50,16 +52,30 @@ class RoutedExperts(FeedForward):
         if len({w.dtype for w in ws}) > 1:
             ws = [w.to(torch.float32) for w in ws]
         # [E][2F][width]: an expert's gate rows, then its up rows; [E][width][F]
-        self.w_gate_up = torch.stack([torch.cat([ws[3 * e], ws[3 * e + 1]], dim=0) for e in range(self.E)]).contiguous()
-        self.w_down = torch.stack([ws[3 * e + 2] for e in range(self.E)]).contiguous()
+        gate_up = torch.stack([torch.cat([ws[3 * e], ws[3 * e + 1]], dim=0) for e in range(self.E)]).contiguous()
+        down = torch.stack([ws[3 * e + 2] for e in range(self.E)]).contiguous()
         del ws
+        self._nbytes = (gate_up.numel() + down.numel()) * down.element_size()
+        # bfloat16 serving: the tensor-core product over rows sorted by expert, on matrices re-laid tile by tile
+        self.tensor_cores = (linear_tc.ENABLED and rt.act_dtype == torch.bfloat16 and down.dtype == torch.bfloat16 and down.is_cuda
+                             and self.width % 8 == 0 and self.inner % 8 == 0)
+        if self.tensor_cores:
+            self.w_gate_up = kernels.pack_weight_groups(gate_up, halves=2)
+            self.w_down = kernels.pack_weight_groups(down)
+        else:
+            self.w_gate_up, self.w_down = gate_up, down
         if self.shared is not None:
             self.shared.bind(tensors, rt)
 
     def weight_bytes(self):
         # a step reads the router, the shared expert, and at most all experts
-        own = self.router.nbytes() + (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
-        return own + (self.shared.weight_bytes() if self.shared is not None else 0)
+        return self.router.nbytes() + self._nbytes + (self.shared.weight_bytes() if self.shared is not None else 0)
+
+    @staticmethod
+    def _row_tile(pairs: int, experts: int) -> int:
+        """Rows per tile of the tensor-core product: about what an expert gets when the choices spread evenly."""
+        avg = pairs / experts
+        return 16 if avg <= 16 else (32 if avg <= 32 else (64 if avg <= 64 else 128))
 
     def forward(self, ctx, h, x):
         n, top, E = h.shape[0], self.top, self.E
@@ -69,15 +85,23 @@ class RoutedExperts(FeedForward):
         ids = ctx.buf("moe_ids", (n, top), torch.int32)
         wts = ctx.buf("moe_weights", (n, top), torch.float32)
         kernels.route_topk(z, ids, wts, top)
-        row_pair = ctx.buf("moe_row_pair", (pairs,), torch.int32)
+        align = self._row_tile(pairs, E) if self.tensor_cores else kernels.moe_tile_rows()
+        max_tiles = kernels.moe_max_tiles(pairs, E, align)
+        rows = max_tiles * align
+        row_src = ctx.buf("moe_row_src", (rows,), torch.int32)
         pair_row = ctx.buf("moe_pair_row", (pairs,), torch.int32)
-        tile_info = ctx.buf("moe_tiles", (3 * kernels.moe_max_tiles(pairs, E),), torch.int32)
-        counts = ctx.buf("moe_counts", (4,), torch.int32)
-        kernels.moe_plan(ids, row_pair, pair_row, tile_info, counts, E)
-        y = ctx.buf("moe_act", (pairs, self.inner), ctx.act_dtype)
-        kernels.moe_gemm(h, self.w_gate_up, y, row_pair, tile_info, counts, pairs, top, True, self.act, self.limit)
-        zz = ctx.buf("moe_out", (pairs, self.width), torch.float32)
-        kernels.moe_gemm(y, self.w_down, zz, row_pair, tile_info, counts, pairs, top, False)
+        tile_group = ctx.buf("moe_tile_group", (max_tiles,), torch.int32)
+        kernels.moe_plan(ids, row_src, pair_row, tile_group, E, align)
+        y = ctx.buf("moe_act", (rows, self.inner), ctx.act_dtype)
+        zz = ctx.buf("moe_out", (rows, self.width), torch.float32)
+        if self.tensor_cores:
+            xs = ctx.buf("moe_rows", (rows, self.width), ctx.act_dtype)
+            kernels.moe_gather(h, xs, row_src, tile_group, top, align)
+            kernels.gemm_tc_grouped(xs, self.w_gate_up, y, tile_group, align, self.inner, kernels.EPI_GATED, self.act, self.limit)
+            kernels.gemm_tc_grouped(y, self.w_down, zz, tile_group, align, self.width)
+        else:
+            kernels.moe_gemm(h, self.w_gate_up, y, row_src, tile_group, top, True, self.act, self.limit)
+            kernels.moe_gemm(y, self.w_down, zz, row_src, tile_group, top, False)
         ctx.materialize(x)
         kernels.moe_combine(x, zz, wts, pair_row, top)
         if self.shared is not None:
