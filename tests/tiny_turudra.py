@@ -59,8 +59,17 @@ CONFIGS = {
             "layers": [_layer(_mlstm(4, 8, 8, 12.0), None),
                        _layer(_mlstm(2, 16, 24, 8.0), _moe(4, 4, 16, 2.5, (16, 2.5)))],
             "loop": {"start": 1, "stop": 2, "times": 2}},
+    # sizes that the tensor-core kernels take (latent sizes 64 and 128, twenty heads = two tiles of sixteen, experts'
+    # widths that are multiples of 8), every expert chosen; scores kept moderate, so that no position hangs on a near tie of two
+    # keys that a bfloat16 rounding can turn
+    "tc": {"architecture": "Turudra", "vocab": 151, "width": 128, "embedding": {"scale": 1.0}, "residual_mult": 0.6,
+           "norm": {"eps": 1e-5}, "logit_softcap": 25.0,
+           "layers": [_layer(_latent(3, 16, 8, 24, 64, 0.08), _moe(4, 4, 32, 2.0, (24, 1.0))),
+                      _layer(_mlstm(2, 16, 32, 10.0), _moe(4, 4, 32, 2.0, None)),
+                      _layer(_latent(20, 8, 16, 8, 128, 0.08, base=1000.0, dims=8), None)],
+           "loop": {"start": 0, "stop": 2, "times": 2}},
 }
-SEEDS = {"mix": 11, "odd": 12, "attn": 13, "rec": 14}
+SEEDS = {"mix": 11, "odd": 12, "attn": 13, "rec": 14, "tc": 16}
 
 
 def shapes(cfg):
@@ -137,3 +146,35 @@ def plain_greedy(cfg, tensors, prompt, n):
     for _ in range(n):
         toks.append(int(np.argmax(plain_logits(cfg, tensors, toks)[-1])))
     return toks[len(prompt):]
+
+
+def recurrence_conditioning(cfg, tensors, tokens, rounding=4e-3):
+    """How far the recurrence's denominator max(|n . q|, exp(-m)) stays above what a rounding of q and k to bfloat16 does
+    to n . q (about `rounding` * |n| |q|), as the smallest ratio over the request's tokens, heads and layer runs.  Where
+    n and q are nearly orthogonal the sum cancels, and below a ratio of about 2 a bfloat16 run legitimately differs from
+    the plain implementation by more than rounding at that token: the design's own conditioning, not the engine's."""
+    import plain_turudra as P
+    worst = [float("inf")]
+    orig = P.mlstm
+
+    def spy(h, w, m, eps, state=None):
+        T, H, D, cap = h.shape[0], m["heads"], m["dim"], m["gate_cap"]
+        q = (h @ w["q"].T).view(T, H, D) * D ** -0.5
+        k = (h @ w["k"].T).view(T, H, D)
+        li = cap * torch.tanh((h @ w["i"].T + w["i.b"]) / cap)
+        lf = torch.nn.functional.logsigmoid(cap * torch.tanh((h @ w["f"].T + w["f.b"]) / cap))
+        n = torch.zeros(H, D, dtype=h.dtype)
+        mx = torch.zeros(H, dtype=h.dtype)
+        for t in range(T):
+            mn = torch.maximum(lf[t] + mx, li[t])
+            n = torch.exp(lf[t] + mx - mn)[:, None] * n + torch.exp(li[t] - mn)[:, None] * k[t]
+            mx = mn
+            den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-mx))
+            worst[0] = min(worst[0], float((den / (rounding * n.norm(dim=-1) * q[t].norm(dim=-1) + 1e-30)).min()))
+        return orig(h, w, m, eps, state)
+    P.mlstm = spy
+    try:
+        P.forward(cfg, {k: v for k, v in tensors.items()}, tokens, dtype=torch.float64)
+    finally:
+        P.mlstm = orig
+    return worst[0]

@@ -159,6 +159,8 @@ XR_EXPORT int xr_head_matmul(const void* in, int in_dtype, long long ld_in, int 
         case XR_F32 * 8 + XR_F32 * 4 + XR_F32 * 2 + XR_F32: HM(float, float, float, float); break;
         case XR_F32 * 8 + XR_F32 * 4 + XR_BF16 * 2 + XR_BF16: HM(float, float, bf, bf); break;
         case XR_BF16 * 8 + XR_F32 * 4 + XR_F32 * 2 + 0: HM(bf, float, float, float); break;
+        case XR_BF16 * 8 + XR_BF16 * 4 + XR_BF16 * 2 + 0: HM(bf, bf, bf, float); break;
+        case XR_BF16 * 8 + XR_F32 * 4 + XR_BF16 * 2 + 0: HM(bf, float, bf, float); break;
         default: return XR_ERR_ARG;
     }
 #undef HM
@@ -273,5 +275,269 @@ XR_EXPORT int xr_latent_attention(const float* ql, const void* qr, int dtype, lo
                   head_qr, out, (const __nv_bfloat16*)cache, page_stride, positions, tok_seg, block_tables, H, C, R, max_pages,
                   page_size, scale);
     } else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same attention on tensor cores (bfloat16, mma.sync m16n8k16 with float32 accumulators), for latent sizes that
+// are multiples of 64 up to 512 and rotated parts that are multiples of 8.
+//
+// A CTA of four warps takes one token and up to sixteen of its heads (the rows of the M = 16 tile: all heads read the
+// same cached rows) over a range of keys, in tiles of 32 keys that cp.async brings to shared memory two deep.
+//   scores   S [16 x 32] = Q [16 x Wp] K^T: warp w takes keys 8w .. 8w + 7 of the tile (Wp = C + R rounded up to 16,
+//            the padding zero on both sides); the scores go to shared memory, times `scale`, keys beyond the range -inf;
+//   softmax  every warp reads S in the layout of the A operand (rows g and g + 8, g = lane / 4), keeps the running
+//            maximum and sum of its rows (the four lanes of a row agree through shuffles) and has P in registers;
+//   sums     O [16 x C] += P [16 x 32] V [32 x C], warp w owning columns w C/4 .. (w+1) C/4; V is the first C columns
+//            of the same rows, read through ldmatrix.trans.
+// grid = (tokens, tiles of 16 heads, splits).  With one split a CTA writes out = O / l; with more, split s takes keys
+// [s chunk, (s+1) chunk) and leaves (m, l, O) in scratch for k_latent_merge, which combines them per (token, head).
+// ---------------------------------------------------------------------------------------------
+#define LT_KT 32
+#define LT_NW 4
+#define LT_MAX_NT 16         // n8 tiles of O per warp: C / 4 / 8 <= 16, so C <= 512
+
+__device__ __forceinline__ uint32_t lt_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void lt_ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lt_ldsm_x2(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void lt_ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void lt_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void lt_cp16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t lt_pack(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// bytes between rows of a tile in shared memory: an odd number of 16-byte units, so that the eight rows an ldmatrix
+// reads lie in different banks
+static __host__ __device__ inline int lt_row_bytes(int Wp) { int u = Wp / 8; return ((u & 1) ? u : u + 1) * 16; }
+
+__global__ void __launch_bounds__(32 * LT_NW)
+k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, const __nv_bfloat16* __restrict__ qr, long long ld_qr, int head_qr,
+                       float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                       const __nv_bfloat16* __restrict__ cache, long long page_stride, const int* __restrict__ positions,
+                       const int* __restrict__ tok_seg, const int* __restrict__ block_tables, int H, int C, int R, int max_pages,
+                       int page_size, float scale, int chunk, int splits) {
+    xr_pdl_launch();
+    extern __shared__ __align__(16) uint8_t lt_sm[];
+    const int W = C + R, Wp = (W + 15) / 16 * 16, rb = lt_row_bytes(Wp);
+    uint8_t* Qs = lt_sm;                                   // [16][rb]
+    uint8_t* Ks = Qs + 16 * rb;                            // [2][32][rb]
+    float* Ss = reinterpret_cast<float*>(Ks + 2 * LT_KT * rb);   // [16][33]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c2 = (lane & 3) * 2;
+    const int t = blockIdx.x, h0 = blockIdx.y * 16, split = blockIdx.z;
+    const int pos = positions[t];
+    const int* bt = block_tables + (size_t)tok_seg[t] * max_pages;
+    const int kbeg = split * chunk, kend = min(pos + 1, kbeg + chunk);       // keys [kbeg, kend)
+    const int mt = gridDim.y;
+    float* my_ml = part_ml + (((size_t)t * mt + blockIdx.y) * splits + split) * 32;
+    float* my_o = part_o + (((size_t)t * mt + blockIdx.y) * splits + split) * 16 * (size_t)C;
+    xr_pdl_wait();
+    if (kend <= kbeg) {                                    // nothing for this split (only with splits > 1)
+        if (threadIdx.x < 16) { my_ml[threadIdx.x * 2] = -INFINITY; my_ml[threadIdx.x * 2 + 1] = 0.f; }
+        return;
+    }
+    // zeros everywhere first: the padding columns stay zero, and rows that a last, partial tile leaves alone hold
+    // finite values (a weight of zero times them must be zero)
+    for (int i = threadIdx.x; i < (16 + 2 * LT_KT) * rb / 16; i += blockDim.x) reinterpret_cast<uint4*>(lt_sm)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    const int n_tiles = (kend - kbeg + LT_KT - 1) / LT_KT;
+    const int chunks16 = W / 8;                            // 16-byte pieces of a cached row
+    auto fetch = [&](int tile, int buf) {
+        const int k0 = kbeg + tile * LT_KT, cnt = min(LT_KT, kend - k0);
+        for (int i = threadIdx.x; i < cnt * chunks16; i += blockDim.x) {
+            const int j = i / chunks16, piece = i % chunks16, kp = k0 + j;
+            const __nv_bfloat16* src = cache + (size_t)bt[kp / page_size] * page_stride + (size_t)(kp % page_size) * W + piece * 8;
+            lt_cp16(lt_smem(Ks + ((size_t)buf * LT_KT + j) * rb + piece * 16), src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, 0);
+    // the queries: [latent part | rotated part] of heads h0 .. h0 + 15 (rows of heads that do not exist stay zero)
+    for (int i = threadIdx.x; i < 16 * (W / 2); i += blockDim.x) {
+        const int r = i / (W / 2), e = (i % (W / 2)) * 2, h = h0 + r;
+        if (h >= H) continue;
+        uint32_t v;
+        if (e < C) v = *reinterpret_cast<const uint32_t*>(ql + ((size_t)t * H + h) * C + e);
+        else v = *reinterpret_cast<const uint32_t*>(qr + (size_t)t * ld_qr + (size_t)h * head_qr + (e - C));
+        *reinterpret_cast<uint32_t*>(Qs + (size_t)r * rb + e * 2) = v;
+    }
+    const int DW = C / LT_NW, NT = DW / 8;                 // this warp's columns of O and their n8 tiles
+    float acc[LT_MAX_NT][4];
+#pragma unroll
+    for (int i = 0; i < LT_MAX_NT; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;       // rows g and g + 8
+    const uint32_t q_addr = lt_smem(Qs) + (lane & 15) * rb + (lane >> 4) * 16;
+    for (int tile = 0; tile < n_tiles; tile++) {
+        const int buf = tile & 1;
+        if (tile + 1 < n_tiles) {
+            fetch(tile + 1, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const uint32_t k_base = lt_smem(Ks + (size_t)buf * LT_KT * rb);
+        // ---- scores of keys 8 warp .. 8 warp + 7
+        {
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t k_addr = k_base + (8 * warp + (lane & 7)) * rb + ((lane >> 3) & 1) * 16;
+            for (int ks = 0; ks < Wp / 16; ks++) {
+                uint32_t a[4], b[2];
+                lt_ldsm_x4(a, q_addr + ks * 32);
+                lt_ldsm_x2(b, k_addr + ks * 32);
+                lt_mma(s, a, b[0], b[1]);
+            }
+            const int key = kbeg + tile * LT_KT + 8 * warp + c2;
+            const float s0 = key < kend ? s[0] * scale : -INFINITY, s1 = key + 1 < kend ? s[1] * scale : -INFINITY;
+            const float s2 = key < kend ? s[2] * scale : -INFINITY, s3 = key + 1 < kend ? s[3] * scale : -INFINITY;
+            Ss[g * 33 + 8 * warp + c2] = s0; Ss[g * 33 + 8 * warp + c2 + 1] = s1;
+            Ss[(g + 8) * 33 + 8 * warp + c2] = s2; Ss[(g + 8) * 33 + 8 * warp + c2 + 1] = s3;
+        }
+        __syncthreads();
+        // ---- softmax (every warp for itself): this thread's values of rows g and g + 8, in the A operand's layout
+        float lo[8], hi[8];
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            const int col = 16 * kk + c2;
+            lo[4 * kk] = Ss[g * 33 + col]; lo[4 * kk + 1] = Ss[g * 33 + col + 1];
+            lo[4 * kk + 2] = Ss[g * 33 + col + 8]; lo[4 * kk + 3] = Ss[g * 33 + col + 9];
+            hi[4 * kk] = Ss[(g + 8) * 33 + col]; hi[4 * kk + 1] = Ss[(g + 8) * 33 + col + 1];
+            hi[4 * kk + 2] = Ss[(g + 8) * 33 + col + 8]; hi[4 * kk + 3] = Ss[(g + 8) * 33 + col + 9];
+        }
+        float mx_lo = lo[0], mx_hi = hi[0];
+#pragma unroll
+        for (int i = 1; i < 8; i++) { mx_lo = fmaxf(mx_lo, lo[i]); mx_hi = fmaxf(mx_hi, hi[i]); }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);        // finite: a tile holds at least one key
+        const float corr_lo = __expf(m_lo - mn_lo), corr_hi = __expf(m_hi - mn_hi);
+        float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            lo[i] = __expf(lo[i] - mn_lo); hi[i] = __expf(hi[i] - mn_hi);
+            sum_lo += lo[i]; sum_hi += hi[i];
+        }
+        sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1); sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+        sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1); sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+        l_lo = l_lo * corr_lo + sum_lo; l_hi = l_hi * corr_hi + sum_hi;
+        m_lo = mn_lo; m_hi = mn_hi;
+        uint32_t pa[2][4];
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+            pa[kk][0] = lt_pack(lo[4 * kk], lo[4 * kk + 1]); pa[kk][1] = lt_pack(hi[4 * kk], hi[4 * kk + 1]);
+            pa[kk][2] = lt_pack(lo[4 * kk + 2], lo[4 * kk + 3]); pa[kk][3] = lt_pack(hi[4 * kk + 2], hi[4 * kk + 3]);
+        }
+        // ---- O = O corr + P V over this warp's columns
+        const uint32_t v_addr = k_base + (lane & 15) * rb + (warp * DW + (lane >> 4) * 8) * 2;
+#pragma unroll
+        for (int nt = 0; nt < LT_MAX_NT; nt += 2) {
+            if (nt < NT) {
+                acc[nt][0] *= corr_lo; acc[nt][1] *= corr_lo; acc[nt][2] *= corr_hi; acc[nt][3] *= corr_hi;
+                acc[nt + 1][0] *= corr_lo; acc[nt + 1][1] *= corr_lo; acc[nt + 1][2] *= corr_hi; acc[nt + 1][3] *= corr_hi;
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    uint32_t b[4];
+                    lt_ldsm_x4_trans(b, v_addr + kk * 16 * rb + nt * 16);
+                    lt_mma(acc[nt], pa[kk], b[0], b[1]);
+                    lt_mma(acc[nt + 1], pa[kk], b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();                                   // S and this buffer are free for the tile after next
+    }
+    // ---- results
+    if (splits == 1) {
+        const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
+#pragma unroll
+        for (int nt = 0; nt < LT_MAX_NT; nt++) {
+            if (nt < NT) {
+                const int col = warp * DW + nt * 8 + c2;
+                if (h0 + g < H) *reinterpret_cast<float2*>(out + ((size_t)t * H + h0 + g) * C + col) = make_float2(acc[nt][0] * inv_lo, acc[nt][1] * inv_lo);
+                if (h0 + g + 8 < H) *reinterpret_cast<float2*>(out + ((size_t)t * H + h0 + g + 8) * C + col) = make_float2(acc[nt][2] * inv_hi, acc[nt][3] * inv_hi);
+            }
+        }
+    } else {
+        if (warp == 0 && (lane & 3) == 0) {
+            my_ml[g * 2] = m_lo; my_ml[g * 2 + 1] = l_lo;
+            my_ml[(g + 8) * 2] = m_hi; my_ml[(g + 8) * 2 + 1] = l_hi;
+        }
+#pragma unroll
+        for (int nt = 0; nt < LT_MAX_NT; nt++) {
+            if (nt < NT) {
+                const int col = warp * DW + nt * 8 + c2;
+                *reinterpret_cast<float2*>(my_o + (size_t)g * C + col) = make_float2(acc[nt][0], acc[nt][1]);
+                *reinterpret_cast<float2*>(my_o + (size_t)(g + 8) * C + col) = make_float2(acc[nt][2], acc[nt][3]);
+            }
+        }
+    }
+}
+
+// out[t][h] = sum_s O_s e^(m_s - M) / sum_s l_s e^(m_s - M), M = max_s m_s, over the splits that saw any key; one warp per (t, h)
+__global__ void __launch_bounds__(128)
+k_latent_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out, int n, int H, int C,
+               int mt, int splits) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long idx = (long long)blockIdx.x * 4 + warp;
+    if (idx >= (long long)n * H) return;
+    const int t = (int)(idx / H), h = (int)(idx % H), tile = h / 16, row = h % 16;
+    const float* ml = part_ml + ((size_t)t * mt + tile) * splits * 32 + row * 2;
+    const float* po = part_o + ((size_t)t * mt + tile) * splits * 16 * (size_t)C + (size_t)row * C;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; s++) if (ml[s * 32 + 1] > 0.f) M = fmaxf(M, ml[s * 32]);
+    float L = 0.f;
+    for (int s = 0; s < splits; s++) if (ml[s * 32 + 1] > 0.f) L += ml[s * 32 + 1] * __expf(ml[s * 32] - M);
+    const float inv = 1.0f / L;
+    for (int d = lane; d < C; d += 32) {
+        float v = 0.f;
+        for (int s = 0; s < splits; s++)
+            if (ml[s * 32 + 1] > 0.f) v = fmaf(po[(size_t)s * 16 * C + d], __expf(ml[s * 32] - M), v);
+        out[((size_t)t * H + h) * C + d] = v * inv;
+    }
+}
+
+XR_EXPORT int xr_latent_attention_mma_supported(int C, int R) {
+    const int Wp = (C + R + 15) / 16 * 16;
+    const size_t smem = (size_t)(16 + 2 * LT_KT) * lt_row_bytes(Wp) + 16 * 33 * sizeof(float);
+    return C >= 64 && C % 64 == 0 && C <= 8 * LT_NW * LT_MAX_NT && R % 8 == 0 && smem <= 200 * 1024;
+}
+
+// ql [n][H * C] bfloat16; qr: rotated query parts (bfloat16, head h of token t at qr + t * ld_qr + h * head_qr);
+// out [n][H * C] float32; part_o [n * ceil(H/16) * splits * 16 * C], part_ml [n * ceil(H/16) * splits * 32]: float32
+// scratch (used when splits > 1); chunk: keys per split, a multiple of 32.
+XR_EXPORT int xr_latent_attention_mma(const void* ql, const void* qr, long long ld_qr, int head_qr, float* out, float* part_o,
+                                      float* part_ml, const void* cache, long long page_stride, const int* positions,
+                                      const int* tok_seg, const int* block_tables, int n, int H, int C, int R, int max_pages,
+                                      int page_size, float scale, int chunk, int splits, cudaStream_t stream) {
+    if (n < 1 || H < 1 || !xr_latent_attention_mma_supported(C, R) || page_size < 1 || splits < 1 || chunk < LT_KT || chunk % LT_KT) return XR_ERR_ARG;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return XR_ERR_ARG;
+    if (splits > 65535 || (H + 15) / 16 > 65535) return XR_ERR_ARG;
+    const int Wp = (C + R + 15) / 16 * 16;
+    const size_t smem = (size_t)(16 + 2 * LT_KT) * lt_row_bytes(Wp) + 16 * 33 * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(k_latent_attention_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return XR_ERR_LAUNCH;
+        configured = true;
+    }
+    const int mt = (H + 15) / 16;
+    xr_launch(k_latent_attention_mma, dim3(n, mt, splits), dim3(32 * LT_NW), smem, stream, (const __nv_bfloat16*)ql, (const __nv_bfloat16*)qr,
+              ld_qr, head_qr, out, part_o, part_ml, (const __nv_bfloat16*)cache, page_stride, positions, tok_seg, block_tables, H, C, R,
+              max_pages, page_size, scale, chunk, splits);
+    if (splits > 1) {
+        const long long warps = (long long)n * H;
+        xr_launch(k_latent_merge, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, out, n, H, C, mt, splits);
+    }
     return xr_launch_status();
 }

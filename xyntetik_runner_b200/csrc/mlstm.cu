@@ -27,49 +27,70 @@ __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) -
 // state layout per slot: [H][D * V + D + 1]
 __device__ __forceinline__ size_t ml_state_head(int D, int V) { return (size_t)D * V + D + 1; }
 
+// Tokens are staged `stage` at a time by the whole block (their k, q and the two logarithms of the gates, so that the
+// loads and the transcendental functions of a chunk overlap); warp 0 then walks the chunk, every lane owning the
+// elements lane, lane + 32, ... of n, with one shuffle reduction per token for n . q.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 k_mlstm_gates(const T* __restrict__ proj, long long ldp, int q_col, int k_col, const float* __restrict__ gates,
               float* __restrict__ state, float* __restrict__ coef, const int* __restrict__ seg_start,
-              const int* __restrict__ seg_len, const int* __restrict__ seg_slot, int H, int D, int V, float cap) {
+              const int* __restrict__ seg_len, const int* __restrict__ seg_slot, int H, int D, int V, float cap, int stage) {
     xr_pdl_launch();
-    __shared__ float scratch[33];
-    extern __shared__ float nsm[];              // n [D]
+    extern __shared__ float gsm[];
+    float* nsm = gsm;                           // n [D]
+    float* kst = nsm + D;                       // [stage][D]
+    float* qst = kst + (size_t)stage * D;       // [stage][D]
+    float* lg = qst + (size_t)stage * D;        // [stage][2]: log input gate, log forget gate
     const int h = blockIdx.x, seg = blockIdx.y;
     const int start = seg_start[seg], len = seg_len[seg], slot = seg_slot[seg];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     xr_pdl_wait();
     float* st = state + ((size_t)slot * H + h) * ml_state_head(D, V);
     float* n_g = st + (size_t)D * V;
     for (int d = threadIdx.x; d < D; d += blockDim.x) nsm[d] = n_g[d];
     float m = n_g[D];
     const float qs = 1.0f / sqrtf((float)D);
-    __syncthreads();
-    for (int j = 0; j < len; j++) {
-        const int t = start + j;
-        const float ai = gates[(size_t)t * 2 * H + h], af = gates[(size_t)t * 2 * H + H + h];
-        const float li = cap * tanhf(ai / cap);
-        const float lf = ml_logsigmoid(cap * tanhf(af / cap));
-        const float m_new = fmaxf(lf + m, li);
-        const float f = expf(lf + m - m_new), i = expf(li - m_new);
-        const T* row = proj + (size_t)t * ldp;
-        float part = 0.f;
-        for (int d = threadIdx.x; d < D; d += blockDim.x) {
-            const float kd = xr_to_f32<T>(row[k_col + h * D + d]);
-            const float qd = xr_to_f32<T>(row[q_col + h * D + d]) * qs;
-            const float nn = fmaf(f, nsm[d], i * kd);
-            nsm[d] = nn;
-            part = fmaf(nn, qd, part);
+    for (int j0 = 0; j0 < len; j0 += stage) {
+        const int cnt = min(stage, len - j0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < cnt * D; e += blockDim.x) {
+            const int j = e / D, d = e % D;
+            const T* row = proj + (size_t)(start + j0 + j) * ldp;
+            kst[j * D + d] = xr_to_f32<T>(row[k_col + h * D + d]);
+            qst[j * D + d] = xr_to_f32<T>(row[q_col + h * D + d]) * qs;
         }
-        // (a block of one warp needs no barrier: every lane owns its elements of n)
-        const float qn = blockDim.x == 32 ? xr_warp_sum(part) : xr_block_sum(part, scratch);
-        m = m_new;
-        if (threadIdx.x == 0) {
-            float* c = coef + ((size_t)t * H + h) * 3;
-            c[0] = f; c[1] = i; c[2] = fmaxf(fabsf(qn), expf(-m_new)) + 1e-6f;
+        for (int j = threadIdx.x; j < cnt; j += blockDim.x) {
+            const int t = start + j0 + j;
+            const float ai = gates[(size_t)t * 2 * H + h], af = gates[(size_t)t * 2 * H + H + h];
+            lg[2 * j] = cap * tanhf(ai / cap);
+            lg[2 * j + 1] = ml_logsigmoid(cap * tanhf(af / cap));
+        }
+        __syncthreads();
+        if (warp == 0) {
+            for (int j = 0; j < cnt; j++) {
+                const float li = lg[2 * j], lf = lg[2 * j + 1];
+                const float m_new = fmaxf(lf + m, li);
+                const float f = expf(lf + m - m_new), i = expf(li - m_new);
+                float part = 0.f;
+                for (int d = lane; d < D; d += 32) {
+                    const float nn = fmaf(f, nsm[d], i * kst[j * D + d]);
+                    nsm[d] = nn;
+                    part = fmaf(nn, qst[j * D + d], part);
+                }
+                const float qn = xr_warp_sum(part);
+                m = m_new;
+                if (lane == 0) {
+                    float* c = coef + ((size_t)(start + j0 + j) * H + h) * 3;
+                    c[0] = f; c[1] = i; c[2] = fmaxf(fabsf(qn), expf(-m_new)) + 1e-6f;
+                }
+            }
         }
     }
-    for (int d = threadIdx.x; d < D; d += blockDim.x) n_g[d] = nsm[d];
-    if (threadIdx.x == 0) n_g[D] = m;
+    __syncthreads();
+    if (warp == 0) {
+        for (int d = lane; d < D; d += 32) n_g[d] = nsm[d];
+        if (lane == 0) n_g[D] = m;
+    }
 }
 
 template <typename T>
@@ -242,7 +263,11 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
                        const int* seg_len, const int* seg_slot, int n, int n_seg, int H, int D, int V, float cap, float eps,
                        cudaStream_t stream) {
     if (n < 1 || n_seg < 1 || H < 1 || D < 1 || V < 1 || !(cap > 0.f) || n_seg > 65535 || H > 65535) return XR_ERR_ARG;
-    const size_t smem_g = (size_t)D * sizeof(float);
+    // tokens staged at a time by the gates kernel: what fits 44 KB of shared memory beside n, at most 32
+    int stage = (int)((44 * 1024 / sizeof(float) - D) / (2 * (size_t)D + 2));
+    stage = stage > 32 ? 32 : stage;
+    if (stage < 1) return XR_ERR_ARG;
+    const size_t smem_g = ((size_t)D + (size_t)stage * (2 * D + 2)) * sizeof(float);
     const size_t smem_s = ((size_t)D * ML_VS + 2 * (size_t)ML_CHUNK * D + ML_CHUNK * ML_VS + ML_CHUNK * ML_RG * ML_VS + ML_CHUNK * 3) * sizeof(float);
     if (smem_g > 48 * 1024 || smem_s > 220 * 1024) return XR_ERR_ARG;
     dim3 gg(H, n_seg), gs((V + ML_VS - 1) / ML_VS, H, n_seg);
@@ -263,8 +288,8 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
         if (D > 256 && smem_s > 48 * 1024 &&                                                                                                     \
             cudaFuncSetAttribute(k_mlstm_scan_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s) != cudaSuccess)      \
             return XR_ERR_LAUNCH;                                                                                                     \
-        xr_launch((k_mlstm_gates<T>), gg, dim3(D <= 512 ? 32 : 256), smem_g, stream, (const T*)proj, ldp, q_col, k_col, gates, state, coef, seg_start, \
-                  seg_len, seg_slot, H, D, V, cap);                                                                                   \
+        xr_launch((k_mlstm_gates<T>), gg, dim3(128), smem_g, stream, (const T*)proj, ldp, q_col, k_col, gates, state, coef, seg_start, \
+                  seg_len, seg_slot, H, D, V, cap, stage);                                                                            \
         SCAN(T);                                                                                                                      \
         xr_launch((k_mlstm_out<T>), dim3(gb), dim3(128), 0, stream, (const float*)o, (const T*)proj, ldp, g_col, norm_w, (T*)y, n, H, \
                   V, eps);                                                                                                            \

@@ -75,6 +75,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_latent_prep": [_vp, _i, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_head_matmul": [_vp, _i, _ll, _i, _vp, _i, _ll, _ll, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp],
         "xr_latent_attention": [_vp, _vp, _i, _ll, _i, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_latent_attention_mma_supported": [_i, _i],
+        "xr_latent_attention_mma": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
         "xr_mlstm": [_vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
         "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
         "xr_moe_plan": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -678,6 +680,44 @@ def latent_attention(ql: torch.Tensor, proj: torch.Tensor, qr_col: int, head_qr:
                                      tok_seg.data_ptr(), block_tables.data_ptr(), n, H, C, R, max_pages, page_size, float(scale),
                                      _stream()), "latent_attention")
     _count()
+
+
+def latent_attention_mma_supported(dtype: torch.dtype, D: int, R: int, C: int) -> bool:
+    """Whether the tensor-core kernel takes these sizes: bfloat16, latent size a multiple of 64 up to 512, rotated part
+    a multiple of 8, an even plain part (the query's pieces are read in pairs)."""
+    return dtype == torch.bfloat16 and D % 2 == 0 and bool(lib().xr_latent_attention_mma_supported(C, R))
+
+
+def latent_attention_splits(n: int, H: int, max_kv_len: int, sms: int = 148) -> tuple:
+    """(keys per split, splits) for a step of n tokens whose longest context is max_kv_len: one split when the tokens
+    alone fill the machine twice, else ranges of at least 128 keys, a multiple of 32."""
+    base = n * (-(-H // 16))
+    if base >= 2 * sms or max_kv_len <= 128:
+        return max(32, -(-max_kv_len // 32) * 32), 1
+    splits = max(1, min(-(-2 * sms // base), -(-max_kv_len // 128)))
+    chunk = -(-(-(-max_kv_len // splits)) // 32) * 32
+    return chunk, -(-max_kv_len // chunk)
+
+
+def latent_attention_mma(ql: torch.Tensor, proj: torch.Tensor, qr_col: int, head_qr: int, out: torch.Tensor,
+                         part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], cache_ptr: int, page_stride: int,
+                         positions, tok_seg, block_tables, H: int, C: int, R: int, max_pages: int, page_size: int, scale: float,
+                         chunk: int, splits: int) -> None:
+    """``latent_attention`` on tensor cores: ql [n, H * C] bfloat16, the cache bfloat16, out [n, H * C] float32.  With
+    `splits` > 1 every range of `chunk` keys is a CTA of its own and part_o [n * ceil(H/16) * splits * 16 * C] and part_ml
+    [n * ceil(H/16) * splits * 32] (float32) carry their results to the kernel that merges them."""
+    _dev(ql, out, positions, tok_seg, block_tables, part_o, part_ml)
+    n = ql.shape[0]
+    mt = -(-H // 16)
+    assert ql.dtype == torch.bfloat16 and proj.dtype == torch.bfloat16 and out.dtype == torch.float32
+    assert ql.shape == (n, H * C) and out.shape == (n, H * C)
+    if splits > 1:
+        assert part_o.numel() >= n * mt * splits * 16 * C and part_ml.numel() >= n * mt * splits * 32
+    _check(lib().xr_latent_attention_mma(ql.data_ptr(), proj.data_ptr() + qr_col * 2, proj.stride(0), head_qr, out.data_ptr(),
+                                         _ptr(part_o), _ptr(part_ml), cache_ptr, page_stride, positions.data_ptr(),
+                                         tok_seg.data_ptr(), block_tables.data_ptr(), n, H, C, R, max_pages, page_size, float(scale),
+                                         chunk, splits, _stream()), "latent_attention_mma")
+    _count(2 if splits > 1 else 1)
 
 
 # ---------------------------------------------------------------------------

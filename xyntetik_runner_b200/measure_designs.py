@@ -55,6 +55,7 @@ FAMILIES = {
     "finish_plain": "products (tcgen05)", "finish_add_rmsnorm": "norms", "rmsnorm": "norms", "finish_rope_store": "rotation + cache store",
     "rope_store": "rotation + cache store", "attention_tc": "attention", "attention_mma": "attention", "attention_simt": "attention",
     "latent_prep": "rotation + cache store", "head_matmul": "latent attention: per-head products", "latent_attention": "latent attention: scores and sums",
+    "latent_attention_mma": "latent attention: scores and sums", "gemm_tc_grouped": "experts' products", "moe_gather": "experts' products",
     "mlstm": "mlstm recurrence", "route_topk": "routing", "moe_plan": "routing", "moe_gemm": "experts' products", "moe_combine": "experts' sum",
     "scaled_add": "stream kernels", "concat_cast": "stream kernels", "softcap": "stream kernels", "embed": "stream kernels", "act_mul": "stream kernels",
 }

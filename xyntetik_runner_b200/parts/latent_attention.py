@@ -24,6 +24,11 @@ from .base import KVNeed, Mixer, PositionEncoding, register_mixer
 from .linear import Linear
 
 
+# the tensor-core kernel for the sizes it takes (a module attribute, so that a test can compare the two kernels)
+USE_MMA = True
+counters = {"mma": 0, "simt": 0}
+
+
 class LatentAttention(Mixer):
     graph_safe = True
 
@@ -88,12 +93,26 @@ class LatentAttention(Mixer):
         kernels.latent_prep(proj, q_cols, ctx.positions, ctx.tok_seg, bt, self.freq, self.norm_w,
                             cache_ptr if lay.writes_cache else None, page_stride, H, D, R, C, self.rot_dims,
                             ctx.max_pages, ctx.page_size, self.eps)
-        ql = ctx.buf("latent_q", (n, H * C), torch.float32)
-        # the plain query parts, taken through W_uk^T into the latent space
-        kernels.head_matmul(proj, 0, D + R, self.w_uk, False, ql, n, H, D, C)
         ol = ctx.buf("latent_o", (n, H * C), torch.float32)
-        kernels.latent_attention(ql, proj, D, D + R, ol, cache_ptr, page_stride, ctx.positions, ctx.tok_seg, bt, H, C, R,
-                                 ctx.max_pages, ctx.page_size, self.scale)
+        if USE_MMA and kernels.latent_attention_mma_supported(ctx.act_dtype, D, R, C):
+            # the plain query parts, taken through W_uk^T into the latent space (bfloat16: an operand of the tensor cores)
+            ql = ctx.buf("latent_q", (n, H * C), torch.bfloat16)
+            kernels.head_matmul(proj, 0, D + R, self.w_uk, False, ql, n, H, D, C)
+            chunk, splits = ctx.once(("latent_splits", H), lambda: kernels.latent_attention_splits(n, H, ctx.max_kv_len))
+            po = pm = None
+            if splits > 1:
+                mt = -(-H // 16)
+                po = ctx.buf("latent_part_o", (n * mt * splits * 16 * C,), torch.float32)
+                pm = ctx.buf("latent_part_ml", (n * mt * splits * 32,), torch.float32)
+            kernels.latent_attention_mma(ql, proj, D, D + R, ol, po, pm, cache_ptr, page_stride, ctx.positions, ctx.tok_seg, bt,
+                                         H, C, R, ctx.max_pages, ctx.page_size, self.scale, chunk, splits)
+            counters["mma"] += 1
+        else:
+            ql = ctx.buf("latent_q", (n, H * C), torch.float32)
+            kernels.head_matmul(proj, 0, D + R, self.w_uk, False, ql, n, H, D, C)
+            kernels.latent_attention(ql, proj, D, D + R, ol, cache_ptr, page_stride, ctx.positions, ctx.tok_seg, bt, H, C, R,
+                                     ctx.max_pages, ctx.page_size, self.scale)
+            counters["simt"] += 1
         o = ctx.buf("attn_out", (n, H * V), ctx.act_dtype)
         kernels.head_matmul(ol, 0, C, self.w_uv, True, o, n, H, C, V, gate=proj if self.gated else None, gate_col=q_cols + C + R)
         ctx.set_pending(x, self.out.forward(o, x, accumulate=True, defer=True))
