@@ -323,8 +323,10 @@ __device__ __forceinline__ uint32_t lt_pack(float a, float b) {
 static __host__ __device__ inline int lt_row_bytes(int Wp) { int u = Wp / 8; return ((u & 1) ? u : u + 1) * 16; }
 
 __global__ void __launch_bounds__(32 * LT_NW)
-k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, const __nv_bfloat16* __restrict__ qr, long long ld_qr, int head_qr,
-                       float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, long long ql_tok, long long ql_head,
+                       const __nv_bfloat16* __restrict__ qr, long long ld_qr, int head_qr,
+                       float* __restrict__ out, __nv_bfloat16* __restrict__ out_h, long long oh_tok, long long oh_head,
+                       float* __restrict__ part_o, float* __restrict__ part_ml,
                        const __nv_bfloat16* __restrict__ cache, long long page_stride, const int* __restrict__ positions,
                        const int* __restrict__ tok_seg, const int* __restrict__ block_tables, int H, int C, int R, int max_pages,
                        int page_size, float scale, int chunk, int splits) {
@@ -368,7 +370,7 @@ k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, const __nv_bfloat16
         const int r = i / (W / 2), e = (i % (W / 2)) * 2, h = h0 + r;
         if (h >= H) continue;
         uint32_t v;
-        if (e < C) v = *reinterpret_cast<const uint32_t*>(ql + ((size_t)t * H + h) * C + e);
+        if (e < C) v = *reinterpret_cast<const uint32_t*>(ql + (size_t)t * ql_tok + (size_t)h * ql_head + e);
         else v = *reinterpret_cast<const uint32_t*>(qr + (size_t)t * ld_qr + (size_t)h * head_qr + (e - C));
         *reinterpret_cast<uint32_t*>(Qs + (size_t)r * rb + e * 2) = v;
     }
@@ -463,8 +465,13 @@ k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, const __nv_bfloat16
         for (int nt = 0; nt < LT_MAX_NT; nt++) {
             if (nt < NT) {
                 const int col = warp * DW + nt * 8 + c2;
-                if (h0 + g < H) *reinterpret_cast<float2*>(out + ((size_t)t * H + h0 + g) * C + col) = make_float2(acc[nt][0] * inv_lo, acc[nt][1] * inv_lo);
-                if (h0 + g + 8 < H) *reinterpret_cast<float2*>(out + ((size_t)t * H + h0 + g + 8) * C + col) = make_float2(acc[nt][2] * inv_hi, acc[nt][3] * inv_hi);
+                if (out_h != nullptr) {
+                    if (h0 + g < H) *reinterpret_cast<uint32_t*>(out_h + (size_t)t * oh_tok + (size_t)(h0 + g) * oh_head + col) = lt_pack(acc[nt][0] * inv_lo, acc[nt][1] * inv_lo);
+                    if (h0 + g + 8 < H) *reinterpret_cast<uint32_t*>(out_h + (size_t)t * oh_tok + (size_t)(h0 + g + 8) * oh_head + col) = lt_pack(acc[nt][2] * inv_hi, acc[nt][3] * inv_hi);
+                } else {
+                    if (h0 + g < H) *reinterpret_cast<float2*>(out + ((size_t)t * H + h0 + g) * C + col) = make_float2(acc[nt][0] * inv_lo, acc[nt][1] * inv_lo);
+                    if (h0 + g + 8 < H) *reinterpret_cast<float2*>(out + ((size_t)t * H + h0 + g + 8) * C + col) = make_float2(acc[nt][2] * inv_hi, acc[nt][3] * inv_hi);
+                }
             }
         }
     } else {
@@ -485,8 +492,8 @@ k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, const __nv_bfloat16
 
 // out[t][h] = sum_s O_s e^(m_s - M) / sum_s l_s e^(m_s - M), M = max_s m_s, over the splits that saw any key; one warp per (t, h)
 __global__ void __launch_bounds__(128)
-k_latent_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out, int n, int H, int C,
-               int mt, int splits) {
+k_latent_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out,
+               __nv_bfloat16* __restrict__ out_h, long long oh_tok, long long oh_head, int n, int H, int C, int mt, int splits) {
     xr_pdl_launch();
     xr_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -504,7 +511,8 @@ k_latent_merge(const float* __restrict__ part_o, const float* __restrict__ part_
         float v = 0.f;
         for (int s = 0; s < splits; s++)
             if (ml[s * 32 + 1] > 0.f) v = fmaf(po[(size_t)s * 16 * C + d], __expf(ml[s * 32] - M), v);
-        out[((size_t)t * H + h) * C + d] = v * inv;
+        if (out_h != nullptr) out_h[(size_t)t * oh_tok + (size_t)h * oh_head + d] = __float2bfloat16_rn(v * inv);
+        else out[((size_t)t * H + h) * C + d] = v * inv;
     }
 }
 
@@ -514,15 +522,18 @@ XR_EXPORT int xr_latent_attention_mma_supported(int C, int R) {
     return C >= 64 && C % 64 == 0 && C <= 8 * LT_NW * LT_MAX_NT && R % 8 == 0 && smem <= 200 * 1024;
 }
 
-// ql [n][H * C] bfloat16; qr: rotated query parts (bfloat16, head h of token t at qr + t * ld_qr + h * head_qr);
+// ql: the queries in the latent space, bfloat16, head h of token t at ql + t * ql_tok + h * ql_head (elements); the result
+// goes to out [n][H * C] float32, or, when out_h is given, as bfloat16 to out_h + t * oh_tok + h * oh_head.
+// qr: rotated query parts (bfloat16, head h of token t at qr + t * ld_qr + h * head_qr);
 // out [n][H * C] float32; part_o [n * ceil(H/16) * splits * 16 * C], part_ml [n * ceil(H/16) * splits * 32]: float32
 // scratch (used when splits > 1); chunk: keys per split, a multiple of 32.
-XR_EXPORT int xr_latent_attention_mma(const void* ql, const void* qr, long long ld_qr, int head_qr, float* out, float* part_o,
-                                      float* part_ml, const void* cache, long long page_stride, const int* positions,
+XR_EXPORT int xr_latent_attention_mma(const void* ql, long long ql_tok, long long ql_head, const void* qr, long long ld_qr, int head_qr,
+                                      float* out, void* out_h, long long oh_tok, long long oh_head, float* part_o, float* part_ml, const void* cache, long long page_stride, const int* positions,
                                       const int* tok_seg, const int* block_tables, int n, int H, int C, int R, int max_pages,
                                       int page_size, float scale, int chunk, int splits, cudaStream_t stream) {
     if (n < 1 || H < 1 || !xr_latent_attention_mma_supported(C, R) || page_size < 1 || splits < 1 || chunk < LT_KT || chunk % LT_KT) return XR_ERR_ARG;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return XR_ERR_ARG;
+    if ((ql_tok | ql_head | oh_tok | oh_head) & 1) return XR_ERR_ARG;            // pairs of bfloat16 are read and written
     if (splits > 65535 || (H + 15) / 16 > 65535) return XR_ERR_ARG;
     const int Wp = (C + R + 15) / 16 * 16;
     const size_t smem = (size_t)(16 + 2 * LT_KT) * lt_row_bytes(Wp) + 16 * 33 * sizeof(float);
@@ -532,12 +543,59 @@ XR_EXPORT int xr_latent_attention_mma(const void* ql, const void* qr, long long 
         configured = true;
     }
     const int mt = (H + 15) / 16;
-    xr_launch(k_latent_attention_mma, dim3(n, mt, splits), dim3(32 * LT_NW), smem, stream, (const __nv_bfloat16*)ql, (const __nv_bfloat16*)qr,
-              ld_qr, head_qr, out, part_o, part_ml, (const __nv_bfloat16*)cache, page_stride, positions, tok_seg, block_tables, H, C, R,
+    xr_launch(k_latent_attention_mma, dim3(n, mt, splits), dim3(32 * LT_NW), smem, stream, (const __nv_bfloat16*)ql, ql_tok, ql_head,
+              (const __nv_bfloat16*)qr, ld_qr, head_qr, out, (__nv_bfloat16*)out_h, oh_tok, oh_head, part_o, part_ml, (const __nv_bfloat16*)cache, page_stride, positions, tok_seg, block_tables, H, C, R,
               max_pages, page_size, scale, chunk, splits);
     if (splits > 1) {
         const long long warps = (long long)n * H;
-        xr_launch(k_latent_merge, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, out, n, H, C, mt, splits);
+        xr_launch(k_latent_merge, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, out, (__nv_bfloat16*)out_h, oh_tok, oh_head, n, H, C, mt, splits);
     }
+    return xr_launch_status();
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Head-major copies around the per-head products on tensor cores (the grouped product wants the rows of one head
+// together, n_pad rows a head):
+//   gather:   out[h * n_pad + t][k] = in[t][h * head_in + k], k < Kd (rows t >= n: zeros)
+//   scatter:  y[t][h * J + j] = in[h * n_pad + t][j] * sigmoid(gate[t][h])     (in: the product's float32 sums, rounded once here)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+k_heads_gather(const __nv_bfloat16* __restrict__ in, long long ld_in, int head_in, __nv_bfloat16* __restrict__ out, int n, int n_pad, int Kd) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y;
+    __nv_bfloat16* o = out + ((size_t)h * n_pad + t) * Kd;
+    if (t >= n) {
+        for (int k = threadIdx.x; k < Kd; k += blockDim.x) o[k] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const __nv_bfloat16* a = in + (size_t)t * ld_in + (size_t)h * head_in;
+    for (int k = threadIdx.x; k < Kd; k += blockDim.x) o[k] = a[k];
+}
+
+__global__ void __launch_bounds__(128)
+k_heads_scatter_gate(const float* __restrict__ in, __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ gate,
+                     long long ld_gate, int n_pad, int H, int J) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float g = gate != nullptr ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * ld_gate + h]))) : 1.0f;
+    const float* a = in + ((size_t)h * n_pad + t) * J;
+    __nv_bfloat16* o = y + ((size_t)t * H + h) * J;
+    for (int j = threadIdx.x; j < J; j += blockDim.x) o[j] = __float2bfloat16_rn(a[j] * g);
+}
+
+XR_EXPORT int xr_heads_gather(const void* in, long long ld_in, int head_in, void* out, int n, int n_pad, int H, int Kd, cudaStream_t stream) {
+    if (n < 1 || n_pad < n || H < 1 || H > 65535 || Kd < 1) return XR_ERR_ARG;
+    xr_launch(k_heads_gather, dim3(n_pad, H), dim3(128), 0, stream, (const __nv_bfloat16*)in, ld_in, head_in, (__nv_bfloat16*)out, n, n_pad, Kd);
+    return xr_launch_status();
+}
+
+XR_EXPORT int xr_heads_scatter_gate(const void* in, void* y, const void* gate, long long ld_gate, int n, int n_pad, int H, int J,
+                                    cudaStream_t stream) {
+    if (n < 1 || n_pad < n || H < 1 || H > 65535 || J < 1) return XR_ERR_ARG;
+    xr_launch(k_heads_scatter_gate, dim3(n, H), dim3(128), 0, stream, (const float*)in, (__nv_bfloat16*)y, (const __nv_bfloat16*)gate,
+              ld_gate, n_pad, H, J);
     return xr_launch_status();
 }

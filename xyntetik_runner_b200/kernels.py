@@ -76,7 +76,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_head_matmul": [_vp, _i, _ll, _i, _vp, _i, _ll, _ll, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp],
         "xr_latent_attention": [_vp, _vp, _i, _ll, _i, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_latent_attention_mma_supported": [_i, _i],
-        "xr_latent_attention_mma": [_vp, _vp, _ll, _i, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+        "xr_latent_attention_mma": [_vp, _ll, _ll, _vp, _ll, _i, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+        "xr_heads_gather": [_vp, _ll, _i, _vp, _i, _i, _i, _i, _vp],
+        "xr_heads_scatter_gate": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
         "xr_mlstm": [_vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
         "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
         "xr_moe_plan": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -702,22 +704,47 @@ def latent_attention_splits(n: int, H: int, max_kv_len: int, sms: int = 148) -> 
 def latent_attention_mma(ql: torch.Tensor, proj: torch.Tensor, qr_col: int, head_qr: int, out: torch.Tensor,
                          part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], cache_ptr: int, page_stride: int,
                          positions, tok_seg, block_tables, H: int, C: int, R: int, max_pages: int, page_size: int, scale: float,
-                         chunk: int, splits: int) -> None:
-    """``latent_attention`` on tensor cores: ql [n, H * C] bfloat16, the cache bfloat16, out [n, H * C] float32.  With
-    `splits` > 1 every range of `chunk` keys is a CTA of its own and part_o [n * ceil(H/16) * splits * 16 * C] and part_ml
-    [n * ceil(H/16) * splits * 32] (float32) carry their results to the kernel that merges them."""
+                         chunk: int, splits: int, n_pad: Optional[int] = None) -> None:
+    """``latent_attention`` on tensor cores, bfloat16 queries and cache.  Token-major (n_pad None): ql [n, H * C], out
+    [n, H * C] float32.  Head-major (n_pad given): ql and out are [H * n_pad, C] bfloat16, head h of token t in row
+    h * n_pad + t (the layout of the grouped per-head products).  With `splits` > 1 every range of `chunk` keys is a
+    CTA of its own and part_o [n * ceil(H/16) * splits * 16 * C] and part_ml [n * ceil(H/16) * splits * 32] (float32)
+    carry their results to the kernel that merges them."""
     _dev(ql, out, positions, tok_seg, block_tables, part_o, part_ml)
-    n = ql.shape[0]
+    n = positions.numel()
     mt = -(-H // 16)
-    assert ql.dtype == torch.bfloat16 and proj.dtype == torch.bfloat16 and out.dtype == torch.float32
-    assert ql.shape == (n, H * C) and out.shape == (n, H * C)
+    assert ql.dtype == torch.bfloat16 and proj.dtype == torch.bfloat16
+    if n_pad is None:
+        assert out.dtype == torch.float32 and ql.shape == (n, H * C) and out.shape == (n, H * C)
+        q_tok, q_head, o32, o16, o_tok, o_head = H * C, C, out.data_ptr(), None, 0, 0
+    else:
+        assert out.dtype == torch.bfloat16 and ql.shape == (H * n_pad, C) and out.shape == (H * n_pad, C) and n_pad >= n
+        q_tok, q_head, o32, o16, o_tok, o_head = C, n_pad * C, None, out.data_ptr(), C, n_pad * C
     if splits > 1:
         assert part_o.numel() >= n * mt * splits * 16 * C and part_ml.numel() >= n * mt * splits * 32
-    _check(lib().xr_latent_attention_mma(ql.data_ptr(), proj.data_ptr() + qr_col * 2, proj.stride(0), head_qr, out.data_ptr(),
-                                         _ptr(part_o), _ptr(part_ml), cache_ptr, page_stride, positions.data_ptr(),
+    _check(lib().xr_latent_attention_mma(ql.data_ptr(), q_tok, q_head, proj.data_ptr() + qr_col * 2, proj.stride(0), head_qr, o32, o16,
+                                         o_tok, o_head, _ptr(part_o), _ptr(part_ml), cache_ptr, page_stride, positions.data_ptr(),
                                          tok_seg.data_ptr(), block_tables.data_ptr(), n, H, C, R, max_pages, page_size, float(scale),
                                          chunk, splits, _stream()), "latent_attention_mma")
     _count(2 if splits > 1 else 1)
+
+
+def heads_gather(inp: torch.Tensor, in_col: int, head_in: int, out: torch.Tensor, n: int, n_pad: int, H: int, Kd: int) -> None:
+    """out[h * n_pad + t] = inp[t, in_col + h * head_in : ... + Kd] (bfloat16; rows t >= n are zeros)."""
+    _dev(out)
+    assert inp.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape == (H * n_pad, Kd) and inp.stride(1) == 1
+    _check(lib().xr_heads_gather(inp.data_ptr() + 2 * in_col, inp.stride(0), head_in, out.data_ptr(), n, n_pad, H, Kd, _stream()), "heads_gather")
+    _count()
+
+
+def heads_scatter_gate(inp: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], gate_col: int, n: int, n_pad: int, H: int, J: int) -> None:
+    """y[t, h * J + j] = inp[h * n_pad + t, j] * sigmoid(gate[t, gate_col + h]) (inp float32, y and gate bfloat16)."""
+    _dev(inp, y)
+    assert inp.dtype == torch.float32 and y.dtype == torch.bfloat16 and inp.shape == (H * n_pad, J) and y.shape == (n, H * J)
+    gptr = None if gate is None else gate.data_ptr() + 2 * gate_col
+    _check(lib().xr_heads_scatter_gate(inp.data_ptr(), y.data_ptr(), gptr, 0 if gate is None else gate.stride(0), n, n_pad, H, J, _stream()),
+           "heads_scatter_gate")
+    _count()
 
 
 # ---------------------------------------------------------------------------

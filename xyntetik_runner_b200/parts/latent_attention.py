@@ -21,6 +21,7 @@ import torch
 from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import KVNeed, Mixer, PositionEncoding, register_mixer
+from . import linear_tc
 from .linear import Linear
 
 
@@ -41,6 +42,7 @@ class LatentAttention(Mixer):
         self.scale, self.position, self.eps, self.prefix, self.gated = float(scale), position, float(eps), prefix, gated
         self.names = {k: prefix + v for k, v in dict(q=q, dkv=dkv, norm=dkv_norm, uk=uk, uv=uv, g=g, o=o).items()}
         self.proj = self.out = self.w_uk = self.w_uv = self.norm_w = self.freq = None
+        self.w_uk_packed = self.w_uv_packed = None
         self.rot_dims = 0
 
     def kv_need(self):
@@ -65,6 +67,13 @@ class LatentAttention(Mixer):
         del ws
         self.out = Linear(tensors[n["o"]]).prepare(rt)
         self.w_uk, self.w_uv = tensors[n["uk"]].contiguous(), tensors[n["uv"]].contiguous()
+        # for the tensor-core products per head: W_uk,h^T ([C, D]: the query goes into the latent space) and W_uv,h ([V, C])
+        self.w_uk_packed = self.w_uv_packed = None
+        if (linear_tc.ENABLED and rt.act_dtype == torch.bfloat16 and self.w_uk.dtype == torch.bfloat16 and self.w_uv.dtype == torch.bfloat16
+                and self.w_uk.is_cuda and self.D % 8 == 0 and self.D >= 8 and self.C % 8 == 0):
+            self.w_uk_packed = kernels.pack_weight_groups(self.w_uk.view(self.H, self.D, self.C).transpose(1, 2).contiguous())
+            self.w_uv_packed = kernels.pack_weight_groups(self.w_uv.view(self.H, self.V, self.C))
+        self._heads_of_tiles = {}
         self.norm_w = tensors[n["norm"]].to(torch.float32).contiguous()
         self.position.prepare(rt)
         rot = self.position.rotary()
@@ -76,6 +85,14 @@ class LatentAttention(Mixer):
             f64 = getattr(self.position, "inv_freq64_host", None)
             f64 = rot.inv_freq.double().cpu().numpy() if f64 is None else f64
             self.freq = torch.from_numpy(np.ascontiguousarray(f64, dtype=np.float64)).to(rt.device)
+
+    def _tile_heads(self, tiles_per_head: int, device) -> torch.Tensor:
+        """int32 [H * tiles_per_head]: the head whose matrix a tile of rows meets in the grouped per-head products."""
+        t = self._heads_of_tiles.get(tiles_per_head)
+        if t is None:
+            t = torch.arange(self.H, dtype=torch.int32, device=device).repeat_interleave(tiles_per_head).contiguous()
+            self._heads_of_tiles[tiles_per_head] = t
+        return t
 
     def weight_bytes(self):
         return (self.proj.nbytes() + self.out.nbytes() + self.w_uk.numel() * self.w_uk.element_size()
@@ -93,28 +110,46 @@ class LatentAttention(Mixer):
         kernels.latent_prep(proj, q_cols, ctx.positions, ctx.tok_seg, bt, self.freq, self.norm_w,
                             cache_ptr if lay.writes_cache else None, page_stride, H, D, R, C, self.rot_dims,
                             ctx.max_pages, ctx.page_size, self.eps)
-        ol = ctx.buf("latent_o", (n, H * C), torch.float32)
+        o = ctx.buf("attn_out", (n, H * V), ctx.act_dtype)
+        gate = proj if self.gated else None
         if USE_MMA and kernels.latent_attention_mma_supported(ctx.act_dtype, D, R, C):
-            # the plain query parts, taken through W_uk^T into the latent space (bfloat16: an operand of the tensor cores)
-            ql = ctx.buf("latent_q", (n, H * C), torch.bfloat16)
-            kernels.head_matmul(proj, 0, D + R, self.w_uk, False, ql, n, H, D, C)
             chunk, splits = ctx.once(("latent_splits", H), lambda: kernels.latent_attention_splits(n, H, ctx.max_kv_len))
             po = pm = None
             if splits > 1:
                 mt = -(-H // 16)
                 po = ctx.buf("latent_part_o", (n * mt * splits * 16 * C,), torch.float32)
                 pm = ctx.buf("latent_part_ml", (n * mt * splits * 32,), torch.float32)
-            kernels.latent_attention_mma(ql, proj, D, D + R, ol, po, pm, cache_ptr, page_stride, ctx.positions, ctx.tok_seg, bt,
-                                         H, C, R, ctx.max_pages, ctx.page_size, self.scale, chunk, splits)
+            args = (cache_ptr, page_stride, ctx.positions, ctx.tok_seg, bt, H, C, R, ctx.max_pages, ctx.page_size, self.scale, chunk, splits)
+            if self.w_uk_packed is not None:
+                # the two per-head products on tcgen05: rows of one head together (n_pad a head), one grouped product each
+                bn = 16 if n <= 16 else (32 if n <= 32 else (64 if n <= 64 else 128))
+                n_pad = -(-n // bn) * bn
+                groups = self._tile_heads(n_pad // bn, h.device)
+                qh = ctx.buf("latent_qh", (H * n_pad, D), torch.bfloat16)
+                kernels.heads_gather(proj, 0, D + R, qh, n, n_pad, H, D)
+                ql = ctx.buf("latent_q", (H * n_pad, C), torch.bfloat16)
+                kernels.gemm_tc_grouped(qh, self.w_uk_packed, ql, groups, bn, C)
+                ol = ctx.buf("latent_o", (H * n_pad, C), torch.bfloat16)
+                kernels.latent_attention_mma(ql, proj, D, D + R, ol, po, pm, *args, n_pad=n_pad)
+                oh = ctx.buf("latent_oh", (H * n_pad, V), torch.float32)
+                kernels.gemm_tc_grouped(ol, self.w_uv_packed, oh, groups, bn, V)
+                kernels.heads_scatter_gate(oh, o, gate, q_cols + C + R, n, n_pad, H, V)
+            else:
+                # the plain query parts, taken through W_uk^T into the latent space (bfloat16: an operand of the tensor cores)
+                ql = ctx.buf("latent_q", (n, H * C), torch.bfloat16)
+                kernels.head_matmul(proj, 0, D + R, self.w_uk, False, ql, n, H, D, C)
+                ol = ctx.buf("latent_o", (n, H * C), torch.float32)
+                kernels.latent_attention_mma(ql, proj, D, D + R, ol, po, pm, *args)
+                kernels.head_matmul(ol, 0, C, self.w_uv, True, o, n, H, C, V, gate=gate, gate_col=q_cols + C + R)
             counters["mma"] += 1
         else:
             ql = ctx.buf("latent_q", (n, H * C), torch.float32)
             kernels.head_matmul(proj, 0, D + R, self.w_uk, False, ql, n, H, D, C)
+            ol = ctx.buf("latent_o", (n, H * C), torch.float32)
             kernels.latent_attention(ql, proj, D, D + R, ol, cache_ptr, page_stride, ctx.positions, ctx.tok_seg, bt, H, C, R,
                                      ctx.max_pages, ctx.page_size, self.scale)
+            kernels.head_matmul(ol, 0, C, self.w_uv, True, o, n, H, C, V, gate=gate, gate_col=q_cols + C + R)
             counters["simt"] += 1
-        o = ctx.buf("attn_out", (n, H * V), ctx.act_dtype)
-        kernels.head_matmul(ol, 0, C, self.w_uv, True, o, n, H, C, V, gate=proj if self.gated else None, gate_col=q_cols + C + R)
         ctx.set_pending(x, self.out.forward(o, x, accumulate=True, defer=True))
 
 
