@@ -336,6 +336,8 @@ def main() -> int:
     ap.add_argument("--step-log", default=None, metavar="FILE", help="with --workload mixed: write one line per step to FILE")
     ap.add_argument("--designs", choices=["w1024", "w2048"], default=None,
                     help="instead of the benchmark: prefill and decode of a Turudra model of this size beside a dense Llama of equal size")
+    ap.add_argument("--designs-models", default="turudra,llama", help=argparse.SUPPRESS)
+    ap.add_argument("--designs-phase", choices=["both", "prefill", "decode"], default="both", help=argparse.SUPPRESS)
     ap.add_argument("--kernels", action="store_true", help="print only the per-kernel table (decode at --batch/--context and a 2,048-token prefill)")
     ap.add_argument("--timeline", action="store_true", help="one layer of a decode step kernel by kernel (needs XRB200_TRACE=1)")
     ap.add_argument("--kernel", choices=["gemm", "attention", "sample"], default=None, help="run one kernel alone on synthetic data")
@@ -355,7 +357,8 @@ def main() -> int:
     if args.designs:
         from xyntetik_runner_b200 import measure_designs
         print(json.dumps(measure_designs.compare(args.designs, batch=args.batch, context=min(args.context, 4096),
-                                                 steps=max(1, args.steps), warmup=max(3, args.warmup), root=ROOT)))
+                                                 steps=max(1, args.steps), warmup=max(3, args.warmup), root=ROOT,
+                                                 models=tuple(args.designs_models.split(",")), phase=args.designs_phase)))
         return 0
     if args.workload == "mixed":
         return mixed_workload(args)

@@ -368,3 +368,21 @@ def test_greedy_generation_through_the_entry_point(models, dtype):
             for i, tok in enumerate(g.tokens):
                 lg = tt.plain_logits(cfg, tensors, list(p) + list(g.tokens[:i]))[-1]
                 assert lg.max() - lg[tok] <= 0.06 * np.abs(lg).max()
+
+
+def test_command_line_generates_what_the_plain_implementation_does(models):
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path, cfg, tensors, _, _ = models["rec"]
+    prompt = traces.random_tokens(9, 7, cfg["vocab"])
+    ids = "ids:" + ",".join(str(t) for t in prompt)
+    out = {}
+    for extra in (["--dtype", "float32"], ["--ref"]):
+        r = subprocess.run([sys.executable, os.path.join(root, "bin", "runner"), "-m", path, "-p", ids, "-n", "6", "--ignore-eos"] + extra,
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        out[extra[-1]] = [ln for ln in r.stdout.splitlines() if ln.startswith("ids:")][0]
+    want = "ids:" + ",".join(str(t) for t in tt.plain_greedy(cfg, tensors, prompt, 6))
+    assert out["--ref"] == want and out["float32"] == want, out

@@ -49,7 +49,7 @@ def encode_prompt(text: str, vocab: int):
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="runner", description="generate with a dense Llama model on one B200")
+    ap = argparse.ArgumentParser(prog="runner", description="generate with a model folder of a known architecture (see known_architectures()) on one B200")
     ap.add_argument("-m", dest="model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("-p", dest="prompt", default=None, help="prompt: text (bytes) or ids:1,2,3; \\n etc. are unescaped")
     ap.add_argument("-f", dest="file", default=None, help="read prompt from file (appended after -p text)")
@@ -103,8 +103,29 @@ def run_plain(args) -> int:
         torch.set_num_threads(args.threads)
         os.environ["OMP_NUM_THREADS"] = str(args.threads)
     sys.path.insert(0, tests)
-    from plain_llama import PlainLlama
-    m = PlainLlama(args.model)
+    from .config.base import read_config_json
+    from .config.registry import architecture_name
+    if architecture_name(read_config_json(args.model)) == "Turudra":
+        # the plain implementation of this architecture takes the configuration and the tensors as they are stored
+        import numpy as np
+        import plain_turudra
+        from .weights.safetensors_io import open_model_files
+        tensors = {n: f.get(n).clone() for f in open_model_files(args.model) for n in f.names()}
+        config = read_config_json(args.model)
+
+        class _Plain:
+            cfg = {"vocab_size": config["vocab"]}
+
+            @staticmethod
+            def generate_greedy(tokens, n):
+                toks = list(tokens)
+                for _ in range(n):
+                    toks.append(int(np.argmax(plain_turudra.forward(config, tensors, toks)[-1].numpy())))
+                return toks[len(tokens):]
+        m = _Plain()
+    else:
+        from plain_llama import PlainLlama
+        m = PlainLlama(args.model)
     text = unescape(args.prompt) if args.prompt is not None else ""
     if args.file:
         with open(args.file, "r", encoding="utf-8") as f:

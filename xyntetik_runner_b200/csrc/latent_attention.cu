@@ -356,11 +356,13 @@ k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, long long ql_tok, l
     const int n_tiles = (kend - kbeg + LT_KT - 1) / LT_KT;
     const int chunks16 = W / 8;                            // 16-byte pieces of a cached row
     auto fetch = [&](int tile, int buf) {
+        // a warp per key (its page and row worked out once), the lanes over the row's 16-byte pieces
         const int k0 = kbeg + tile * LT_KT, cnt = min(LT_KT, kend - k0);
-        for (int i = threadIdx.x; i < cnt * chunks16; i += blockDim.x) {
-            const int j = i / chunks16, piece = i % chunks16, kp = k0 + j;
-            const __nv_bfloat16* src = cache + (size_t)bt[kp / page_size] * page_stride + (size_t)(kp % page_size) * W + piece * 8;
-            lt_cp16(lt_smem(Ks + ((size_t)buf * LT_KT + j) * rb + piece * 16), src);
+        for (int j = warp; j < cnt; j += LT_NW) {
+            const int kp = k0 + j;
+            const __nv_bfloat16* src = cache + (size_t)bt[kp / page_size] * page_stride + (size_t)(kp % page_size) * W;
+            const uint32_t dst = lt_smem(Ks + ((size_t)buf * LT_KT + j) * rb);
+            for (int piece = lane; piece < chunks16; piece += 32) lt_cp16(dst + piece * 16, src + piece * 8);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -490,7 +492,8 @@ k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, long long ql_tok, l
     }
 }
 
-// out[t][h] = sum_s O_s e^(m_s - M) / sum_s l_s e^(m_s - M), M = max_s m_s, over the splits that saw any key; one warp per (t, h)
+// out[t][h] = sum_s O_s e^(m_s - M) / sum_s l_s e^(m_s - M), M = max_s m_s, over the splits that saw any key; one warp per
+// (t, h): the lanes first hold one split each (its weight e^(m_s - M), zero for a split without keys), then one column each
 __global__ void __launch_bounds__(128)
 k_latent_merge(const float* __restrict__ part_o, const float* __restrict__ part_ml, float* __restrict__ out,
                __nv_bfloat16* __restrict__ out_h, long long oh_tok, long long oh_head, int n, int H, int C, int mt, int splits) {
@@ -503,16 +506,36 @@ k_latent_merge(const float* __restrict__ part_o, const float* __restrict__ part_
     const float* ml = part_ml + ((size_t)t * mt + tile) * splits * 32 + row * 2;
     const float* po = part_o + ((size_t)t * mt + tile) * splits * 16 * (size_t)C + (size_t)row * C;
     float M = -INFINITY;
-    for (int s = 0; s < splits; s++) if (ml[s * 32 + 1] > 0.f) M = fmaxf(M, ml[s * 32]);
+    for (int s = lane; s < splits; s += 32) if (ml[s * 32 + 1] > 0.f) M = fmaxf(M, ml[s * 32]);
+    M = xr_warp_max(M);
     float L = 0.f;
-    for (int s = 0; s < splits; s++) if (ml[s * 32 + 1] > 0.f) L += ml[s * 32 + 1] * __expf(ml[s * 32] - M);
+    for (int s = lane; s < splits; s += 32) if (ml[s * 32 + 1] > 0.f) L += ml[s * 32 + 1] * __expf(ml[s * 32] - M);
+    L = xr_warp_sum(L);
     const float inv = 1.0f / L;
-    for (int d = lane; d < C; d += 32) {
-        float v = 0.f;
-        for (int s = 0; s < splits; s++)
-            if (ml[s * 32 + 1] > 0.f) v = fmaf(po[(size_t)s * 16 * C + d], __expf(ml[s * 32] - M), v);
-        if (out_h != nullptr) out_h[(size_t)t * oh_tok + (size_t)h * oh_head + d] = __float2bfloat16_rn(v * inv);
-        else out[((size_t)t * H + h) * C + d] = v * inv;
+    float acc[LT_MAX_NT];                       // columns lane, lane + 32, ... (C <= 512)
+#pragma unroll
+    for (int i = 0; i < LT_MAX_NT; i++) acc[i] = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        const int mine = s0 + lane;
+        const float w_mine = (mine < splits && ml[mine * 32 + 1] > 0.f) ? __expf(ml[mine * 32] - M) : 0.f;
+        const int cnt = min(32, splits - s0);
+        for (int j = 0; j < cnt; j++) {
+            const float w = __shfl_sync(0xffffffffu, w_mine, j);
+            if (w == 0.f) continue;                    // (the same for the whole warp)
+            const float* src = po + (size_t)(s0 + j) * 16 * C;
+#pragma unroll
+            for (int i = 0; i < LT_MAX_NT; i++) {
+                const int d = lane + 32 * i;
+                if (d < C) acc[i] = fmaf(src[d], w, acc[i]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < LT_MAX_NT; i++) {
+        const int d = lane + 32 * i;
+        if (d >= C) continue;
+        if (out_h != nullptr) out_h[(size_t)t * oh_tok + (size_t)h * oh_head + d] = __float2bfloat16_rn(acc[i] * inv);
+        else out[((size_t)t * H + h) * C + d] = acc[i] * inv;
     }
 }
 

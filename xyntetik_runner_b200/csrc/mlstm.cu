@@ -27,38 +27,36 @@ __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) -
 // state layout per slot: [H][D * V + D + 1]
 __device__ __forceinline__ size_t ml_state_head(int D, int V) { return (size_t)D * V + D + 1; }
 
-// Tokens are staged `stage` at a time by the whole block (their k, q and the two logarithms of the gates, so that the
-// loads and the transcendental functions of a chunk overlap); warp 0 then walks the chunk, every lane owning the
-// elements lane, lane + 32, ... of n, with one shuffle reduction per token for n . q.
+// Tokens are taken `stage` at a time, in four steps a chunk, so that nothing but a few scalar operations per token is
+// serial: (1) the logarithms of the gates of the chunk's tokens, a thread a token; (2) one thread walks the chunk's
+// scalars: m, f, i and exp(-m) of every token; (3) every thread owns elements of n and walks the chunk with them,
+// n <- f n + i k, leaving n[d] q[d] of every token in shared memory; (4) the warps sum those products token by token
+// (always in the same order) and write (f, i, denominator).
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 k_mlstm_gates(const T* __restrict__ proj, long long ldp, int q_col, int k_col, const float* __restrict__ gates,
               float* __restrict__ state, float* __restrict__ coef, const int* __restrict__ seg_start,
               const int* __restrict__ seg_len, const int* __restrict__ seg_slot, int H, int D, int V, float cap, int stage) {
     xr_pdl_launch();
     extern __shared__ float gsm[];
-    float* nsm = gsm;                           // n [D]
-    float* kst = nsm + D;                       // [stage][D]
-    float* qst = kst + (size_t)stage * D;       // [stage][D]
-    float* lg = qst + (size_t)stage * D;        // [stage][2]: log input gate, log forget gate
+    float* prod = gsm;                          // [stage][D]: n[d] q[d] of the chunk's tokens
+    float* lg = prod + (size_t)stage * D;       // [stage][2]: log input gate, log forget gate
+    float* fi = lg + 2 * stage;                 // [stage][3]: f, i, exp(-m)
+    __shared__ float m_run;
     const int h = blockIdx.x, seg = blockIdx.y;
     const int start = seg_start[seg], len = seg_len[seg], slot = seg_slot[seg];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     xr_pdl_wait();
     float* st = state + ((size_t)slot * H + h) * ml_state_head(D, V);
     float* n_g = st + (size_t)D * V;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) nsm[d] = n_g[d];
-    float m = n_g[D];
+    constexpr int OWN = 4;                      // elements of n per thread: D <= 4 * 256
+    float nreg[OWN];
+#pragma unroll
+    for (int i = 0; i < OWN; i++) { const int d = threadIdx.x + i * blockDim.x; nreg[i] = d < D ? n_g[d] : 0.f; }
+    if (threadIdx.x == 0) m_run = n_g[D];
     const float qs = 1.0f / sqrtf((float)D);
     for (int j0 = 0; j0 < len; j0 += stage) {
         const int cnt = min(stage, len - j0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < cnt * D; e += blockDim.x) {
-            const int j = e / D, d = e % D;
-            const T* row = proj + (size_t)(start + j0 + j) * ldp;
-            kst[j * D + d] = xr_to_f32<T>(row[k_col + h * D + d]);
-            qst[j * D + d] = xr_to_f32<T>(row[q_col + h * D + d]) * qs;
-        }
         for (int j = threadIdx.x; j < cnt; j += blockDim.x) {
             const int t = start + j0 + j;
             const float ai = gates[(size_t)t * 2 * H + h], af = gates[(size_t)t * 2 * H + H + h];
@@ -66,31 +64,46 @@ k_mlstm_gates(const T* __restrict__ proj, long long ldp, int q_col, int k_col, c
             lg[2 * j + 1] = ml_logsigmoid(cap * tanhf(af / cap));
         }
         __syncthreads();
-        if (warp == 0) {
+        if (threadIdx.x == 0) {
+            float m = m_run;
             for (int j = 0; j < cnt; j++) {
                 const float li = lg[2 * j], lf = lg[2 * j + 1];
                 const float m_new = fmaxf(lf + m, li);
-                const float f = expf(lf + m - m_new), i = expf(li - m_new);
-                float part = 0.f;
-                for (int d = lane; d < D; d += 32) {
-                    const float nn = fmaf(f, nsm[d], i * kst[j * D + d]);
-                    nsm[d] = nn;
-                    part = fmaf(nn, qst[j * D + d], part);
-                }
-                const float qn = xr_warp_sum(part);
+                fi[3 * j] = expf(lf + m - m_new); fi[3 * j + 1] = expf(li - m_new); fi[3 * j + 2] = expf(-m_new);
                 m = m_new;
-                if (lane == 0) {
-                    float* c = coef + ((size_t)(start + j0 + j) * H + h) * 3;
-                    c[0] = f; c[1] = i; c[2] = fmaxf(fabsf(qn), expf(-m_new)) + 1e-6f;
+            }
+            m_run = m;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < OWN; i++) {
+            const int d = threadIdx.x + i * blockDim.x;
+            if (d < D) {
+                float nn = nreg[i];
+#pragma unroll 8
+                for (int j = 0; j < cnt; j++) {
+                    const T* row = proj + (size_t)(start + j0 + j) * ldp + (size_t)h * D + d;
+                    nn = fmaf(fi[3 * j], nn, fi[3 * j + 1] * xr_to_f32<T>(row[k_col]));
+                    prod[j * D + d] = nn * (xr_to_f32<T>(row[q_col]) * qs);
                 }
+                nreg[i] = nn;
             }
         }
+        __syncthreads();
+        for (int j = warp; j < cnt; j += nw) {
+            float part = 0.f;
+            for (int d = lane; d < D; d += 32) part += prod[j * D + d];
+            const float qn = xr_warp_sum(part);
+            if (lane == 0) {
+                float* c = coef + ((size_t)(start + j0 + j) * H + h) * 3;
+                c[0] = fi[3 * j]; c[1] = fi[3 * j + 1]; c[2] = fmaxf(fabsf(qn), fi[3 * j + 2]) + 1e-6f;
+            }
+        }
+        __syncthreads();
     }
-    __syncthreads();
-    if (warp == 0) {
-        for (int d = lane; d < D; d += 32) n_g[d] = nsm[d];
-        if (lane == 0) n_g[D] = m;
-    }
+#pragma unroll
+    for (int i = 0; i < OWN; i++) { const int d = threadIdx.x + i * blockDim.x; if (d < D) n_g[d] = nreg[i]; }
+    if (threadIdx.x == 0) n_g[D] = m_run;
 }
 
 template <typename T>
@@ -263,11 +276,11 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
                        const int* seg_len, const int* seg_slot, int n, int n_seg, int H, int D, int V, float cap, float eps,
                        cudaStream_t stream) {
     if (n < 1 || n_seg < 1 || H < 1 || D < 1 || V < 1 || !(cap > 0.f) || n_seg > 65535 || H > 65535) return XR_ERR_ARG;
-    // tokens staged at a time by the gates kernel: what fits 44 KB of shared memory beside n, at most 32
-    int stage = (int)((44 * 1024 / sizeof(float) - D) / (2 * (size_t)D + 2));
+    // tokens a chunk of the gates kernel: what fits 44 KB of shared memory, at most 32; its threads own up to 4 elements of n each
+    if (D > 1024) return XR_ERR_ARG;
+    int stage = (int)((44 * 1024 / sizeof(float)) / ((size_t)D + 5));
     stage = stage > 32 ? 32 : stage;
-    if (stage < 1) return XR_ERR_ARG;
-    const size_t smem_g = ((size_t)D + (size_t)stage * (2 * D + 2)) * sizeof(float);
+    const size_t smem_g = (size_t)stage * (D + 5) * sizeof(float);
     const size_t smem_s = ((size_t)D * ML_VS + 2 * (size_t)ML_CHUNK * D + ML_CHUNK * ML_VS + ML_CHUNK * ML_RG * ML_VS + ML_CHUNK * 3) * sizeof(float);
     if (smem_g > 48 * 1024 || smem_s > 220 * 1024) return XR_ERR_ARG;
     dim3 gg(H, n_seg), gs((V + ML_VS - 1) / ML_VS, H, n_seg);
@@ -288,7 +301,7 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
         if (D > 256 && smem_s > 48 * 1024 &&                                                                                                     \
             cudaFuncSetAttribute(k_mlstm_scan_wide<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s) != cudaSuccess)      \
             return XR_ERR_LAUNCH;                                                                                                     \
-        xr_launch((k_mlstm_gates<T>), gg, dim3(128), smem_g, stream, (const T*)proj, ldp, q_col, k_col, gates, state, coef, seg_start, \
+        xr_launch((k_mlstm_gates<T>), gg, dim3(D <= 128 ? 128 : 256), smem_g, stream, (const T*)proj, ldp, q_col, k_col, gates, state, coef, seg_start, \
                   seg_len, seg_slot, H, D, V, cap, stage);                                                                            \
         SCAN(T);                                                                                                                      \
         xr_launch((k_mlstm_out<T>), dim3(gb), dim3(128), 0, stream, (const float*)o, (const T*)proj, ldp, g_col, norm_w, (T*)y, n, H, \

@@ -55,7 +55,9 @@ FAMILIES = {
     "finish_plain": "products (tcgen05)", "finish_add_rmsnorm": "norms", "rmsnorm": "norms", "finish_rope_store": "rotation + cache store",
     "rope_store": "rotation + cache store", "attention_tc": "attention", "attention_mma": "attention", "attention_simt": "attention",
     "latent_prep": "rotation + cache store", "head_matmul": "latent attention: per-head products", "latent_attention": "latent attention: scores and sums",
-    "latent_attention_mma": "latent attention: scores and sums", "gemm_tc_grouped": "experts' products", "moe_gather": "experts' products",
+    "latent_attention_mma": "latent attention: scores and sums", "gemm_tc_grouped": "grouped products (experts, per-head)",
+    "moe_gather": "grouped products (experts, per-head)", "heads_gather": "grouped products (experts, per-head)",
+    "heads_scatter_gate": "grouped products (experts, per-head)",
     "mlstm": "mlstm recurrence", "route_topk": "routing", "moe_plan": "routing", "moe_gemm": "experts' products", "moe_combine": "experts' sum",
     "scaled_add": "stream kernels", "concat_cast": "stream kernels", "softcap": "stream kernels", "embed": "stream kernels", "act_mul": "stream kernels",
 }
@@ -119,6 +121,7 @@ def _work(cfg, tokens: int, keys_per_token: float, decode: bool) -> Dict[str, tu
             by_m += (tokens if decode else 1) * 2 * m.heads * m.dim * m.vdim * 4
             fl_m += 4.0 * tokens * m.heads * m.dim * m.vdim
     out["experts' products"] = (fl_e, by_e)
+    out["grouped products (experts, per-head)"] = (fl_e + fl_h, by_e)
     out["latent attention: scores and sums"] = (fl_a, by_a)
     out["latent attention: per-head products"] = (fl_h, 0.0)
     out["mlstm recurrence"] = (fl_m, by_m)
@@ -135,7 +138,7 @@ def _llama_work(cfg, tokens, keys_per_token, decode):
     return {"attention": (fl_a, by_a), "products (tcgen05)": (fl_p, by_p)}
 
 
-def _measure(eng, cfg, work_fn, tokens: int, batch: int, context: int, steps: int, warmup: int, pk) -> dict:
+def _measure(eng, cfg, work_fn, tokens: int, batch: int, context: int, steps: int, warmup: int, pk, phase: str = "both") -> dict:
     vocab = eng.plan.vocab_size
     gen = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
@@ -144,6 +147,28 @@ def _measure(eng, cfg, work_fn, tokens: int, batch: int, context: int, steps: in
         lg = eng.step([StepEntry("p", prompt, [tokens - 1])])
         eng.end("p")
         return lg
+    out = {"weight_bytes_per_step": eng.weight_bytes_per_step()}
+
+    def table(fam, work):
+        rows = []
+        for name, us in sorted(fam.items(), key=lambda kv: -kv[1]):
+            row = {"kernels": name, "us": round(us, 1)}
+            if name in work and us > 0:
+                fl, by = work[name]
+                row["tflops"] = round(fl / us / 1e6, 2)
+                row["gbs"] = round(by / us / 1e3, 1)
+                row["frac"] = round(max(fl / us / 1e6 / pk["bf16_tflops"], by / us / 1e3 / pk["hbm_gbs"]), 4)
+            rows.append(row)
+        return rows
+    if phase in ("both", "prefill"):
+        out["prefill"] = _prefill(eng, cfg, work_fn, tokens, warmup, prefill_once, table)
+    if phase in ("both", "decode"):
+        out["decode"] = _decode(eng, cfg, work_fn, batch, context, steps, warmup, vocab, gen, table)
+    eng.check_status()
+    return out
+
+
+def _prefill(eng, cfg, work_fn, tokens, warmup, prefill_once, table):
     for _ in range(max(2, warmup // 2)):
         prefill_once()
     torch.cuda.synchronize()
@@ -158,7 +183,12 @@ def _measure(eng, cfg, work_fn, tokens: int, batch: int, context: int, steps: in
     with _Timed() as t:
         prefill_once()
     prefill_fam = t.by_family()
-    # decode
+    return {"tokens": tokens, "ms": round(prefill_ms, 3), "tok_s": round(tokens / prefill_ms * 1e3),
+            "kernels": table(prefill_fam, work_fn(cfg, tokens, (tokens + 1) / 2.0, False))}
+
+
+def _decode(eng, cfg, work_fn, batch, context, steps, warmup, vocab, gen, table):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ids = [f"d{i}" for i in range(batch)]
     for r in ids:
         eng.adopt(r, context)
@@ -183,27 +213,12 @@ def _measure(eng, cfg, work_fn, tokens: int, batch: int, context: int, steps: in
     eng._graph_ok = graphs
     for r in ids:
         eng.end(r)
-    eng.check_status()
-
-    def table(fam, work):
-        rows = []
-        for name, us in sorted(fam.items(), key=lambda kv: -kv[1]):
-            row = {"kernels": name, "us": round(us, 1)}
-            if name in work and us > 0:
-                fl, by = work[name]
-                row["tflops"] = round(fl / us / 1e6, 2)
-                row["gbs"] = round(by / us / 1e3, 1)
-                row["frac"] = round(max(fl / us / 1e6 / pk["bf16_tflops"], by / us / 1e3 / pk["hbm_gbs"]), 4)
-            rows.append(row)
-        return rows
-    return {"prefill": {"tokens": tokens, "ms": round(prefill_ms, 3), "tok_s": round(tokens / prefill_ms * 1e3),
-                        "kernels": table(prefill_fam, work_fn(cfg, tokens, (tokens + 1) / 2.0, False))},
-            "decode": {"batch": batch, "context": context, "ms": round(decode_ms, 4), "tok_s": round(batch / decode_ms * 1e3),
-                       "kernels": table(decode_fam, work_fn(cfg, batch, context + steps / 2.0, True))},
-            "weight_bytes_per_step": eng.weight_bytes_per_step()}
+    return {"batch": batch, "context": context, "ms": round(decode_ms, 4), "tok_s": round(batch / decode_ms * 1e3),
+            "kernels": table(decode_fam, work_fn(cfg, batch, context + steps / 2.0, True))}
 
 
-def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, steps: int = 32, warmup: int = 4, root=None) -> dict:
+def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, steps: int = 32, warmup: int = 4, root=None,
+            models=("turudra", "llama"), phase: str = "both") -> dict:
     pk = measure.peaks(root)
     out = {"size": size, "peaks": pk["source"], "dtype": "bf16", "data": "synthetic: random weights, random tokens"}
     tcfg = turudra_config(size)
@@ -211,12 +226,14 @@ def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, 
     ep = lambda: EngineParams(dtype="bfloat16", max_tokens=pool, page_size=64, max_requests=batch + 1,
                               max_request_tokens=max(tokens, context + steps + warmup + 72), max_step_tokens=tokens)
     for name, cfg, work in (("turudra", tcfg, _work), ("llama", llama_config(size, len(tcfg.layer_runs()), context + tokens), _llama_work)):
+        if name not in models:
+            continue
         t0 = time.perf_counter()
         eng = random_engine(cfg, 5, ep())
         for kv in eng.kv:
             kv.normal_(0.0, 1.0)
         torch.cuda.synchronize()
-        out[name] = _measure(eng, cfg, work, tokens, batch, context, steps, warmup, pk)
+        out[name] = _measure(eng, cfg, work, tokens, batch, context, steps, warmup, pk, phase)
         out[name]["load_s"] = round(time.perf_counter() - t0, 1)
         del eng
         torch.cuda.empty_cache()
