@@ -394,14 +394,32 @@ k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, long long ql_tok, l
         const uint32_t k_base = lt_smem(Ks + (size_t)buf * LT_KT * rb);
         // ---- scores of keys 8 warp .. 8 warp + 7
         {
-            float s[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t k_addr = k_base + (8 * warp + (lane & 7)) * rb + ((lane >> 3) & 1) * 16;
-            for (int ks = 0; ks < Wp / 16; ks++) {
+            // four accumulators and four k steps a round: consecutive MMAs do not wait for one another
+            float s[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f}, sc[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t k_addr = k_base + (8 * warp + (lane & 7)) * rb + ((lane >> 3) & 3) * 16;
+            const int steps = Wp / 16;
+            int ks = 0;
+            for (; ks + 3 < steps; ks += 4) {
+                uint32_t a0[4], a1[4], a2[4], a3[4], b01[4], b23[4];
+                lt_ldsm_x4(b01, k_addr + ks * 32);               // this key tile's columns of two k steps
+                lt_ldsm_x4(b23, k_addr + ks * 32 + 64);
+                lt_ldsm_x4(a0, q_addr + ks * 32);
+                lt_ldsm_x4(a1, q_addr + ks * 32 + 32);
+                lt_ldsm_x4(a2, q_addr + ks * 32 + 64);
+                lt_ldsm_x4(a3, q_addr + ks * 32 + 96);
+                lt_mma(s, a0, b01[0], b01[1]);
+                lt_mma(sb, a1, b01[2], b01[3]);
+                lt_mma(sc, a2, b23[0], b23[1]);
+                lt_mma(sd, a3, b23[2], b23[3]);
+            }
+            for (; ks < steps; ks++) {
                 uint32_t a[4], b[2];
                 lt_ldsm_x4(a, q_addr + ks * 32);
                 lt_ldsm_x2(b, k_addr + ks * 32);
                 lt_mma(s, a, b[0], b[1]);
             }
+#pragma unroll
+            for (int i = 0; i < 4; i++) s[i] = (s[i] + sb[i]) + (sc[i] + sd[i]);
             const int key = kbeg + tile * LT_KT + 8 * warp + c2;
             const float s0 = key < kend ? s[0] * scale : -INFINITY, s1 = key + 1 < kend ? s[1] * scale : -INFINITY;
             const float s2 = key < kend ? s[2] * scale : -INFINITY, s3 = key + 1 < kend ? s[3] * scale : -INFINITY;

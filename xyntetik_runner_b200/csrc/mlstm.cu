@@ -20,7 +20,7 @@
 
 #define ML_VS 32          // value columns per block of the scan
 #define ML_RG 8           // row groups (warps) per block of the scan
-#define ML_CHUNK 8        // tokens whose q, k, v are staged together
+#define ML_CHUNK 8        // tokens whose q, k, v are staged together (the register scan stages one token per warp: = ML_RG)
 
 __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
@@ -195,21 +195,38 @@ k_mlstm_scan(const T* __restrict__ proj, long long ldp, int q_col, int k_col, in
         S[i] = (col_ok && d < D) ? Sg[(size_t)d * V + v0 + col] : 0.f;
     }
     const float qscale = 1.0f / sqrtf((float)D);
+    // the next chunk's k, q, v and scalars are on their way to registers while this chunk is computed
+    constexpr int NL = ML_CHUNK * DP / (ML_VS * ML_RG);           // elements of k (and of q) per thread and chunk
+    T kreg[NL], qreg[NL], vreg = xr_from_f32<T>(0.f);
+    float creg = 0.f;
+    auto prefetch = [&](int j0) {
+        const int cnt = min(ML_CHUNK, len - j0);
+#pragma unroll
+        for (int i = 0; i < NL; i++) {
+            const int e = threadIdx.x + i * (ML_VS * ML_RG), j = e / DP, d = e % DP;
+            const bool ok = j < cnt && d < D;
+            const T* row = proj + (size_t)(start + j0 + (ok ? j : 0)) * ldp + (size_t)h * D + (ok ? d : 0);
+            kreg[i] = ok ? row[k_col] : xr_from_f32<T>(0.f);
+            qreg[i] = ok ? row[q_col] : xr_from_f32<T>(0.f);
+        }
+        const int j = threadIdx.x / ML_VS;
+        vreg = (j < cnt && col_ok) ? proj[(size_t)(start + j0 + j) * ldp + v_col + h * V + v0 + col] : xr_from_f32<T>(0.f);
+        if ((int)threadIdx.x < cnt * 3) creg = coef[((size_t)(start + j0 + threadIdx.x / 3) * H + h) * 3 + threadIdx.x % 3];
+    };
+    prefetch(0);
     for (int j0 = 0; j0 < len; j0 += ML_CHUNK) {
         const int cnt = min(ML_CHUNK, len - j0);
         __syncthreads();
-        for (int e = threadIdx.x; e < cnt * DP; e += blockDim.x) {
-            const int j = e / DP, d = e % DP;
-            const T* row = proj + (size_t)(start + j0 + j) * ldp;
-            ks[j][d] = d < D ? xr_to_f32<T>(row[k_col + h * D + d]) : 0.f;
-            qsm[j][d] = d < D ? xr_to_f32<T>(row[q_col + h * D + d]) * qscale : 0.f;
+#pragma unroll
+        for (int i = 0; i < NL; i++) {
+            const int e = threadIdx.x + i * (ML_VS * ML_RG), j = e / DP, d = e % DP;
+            ks[j][d] = xr_to_f32<T>(kreg[i]);
+            qsm[j][d] = xr_to_f32<T>(qreg[i]) * qscale;
         }
-        for (int e = threadIdx.x; e < cnt * ML_VS; e += blockDim.x) {
-            const int j = e / ML_VS, c = e % ML_VS;
-            vs[j][c] = v0 + c < V ? xr_to_f32<T>(proj[(size_t)(start + j0 + j) * ldp + v_col + h * V + v0 + c]) : 0.f;
-        }
-        for (int e = threadIdx.x; e < cnt * 3; e += blockDim.x) cf[e / 3][e % 3] = coef[((size_t)(start + j0 + e / 3) * H + h) * 3 + e % 3];
+        vs[threadIdx.x / ML_VS][col] = xr_to_f32<T>(vreg);
+        if (threadIdx.x < ML_CHUNK * 3) cf[threadIdx.x / 3][threadIdx.x % 3] = creg;
         __syncthreads();
+        if (j0 + ML_CHUNK < len) prefetch(j0 + ML_CHUNK);
         for (int j = 0; j < cnt; j++) {
             const float f = cf[j][0], iv = cf[j][1] * vs[j][col];
             const float4* k4 = reinterpret_cast<const float4*>(&ks[j][rg * RPT]);
