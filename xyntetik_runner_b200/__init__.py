@@ -1,4 +1,4 @@
-"""A small, whole inference engine for the dense Llama decoder on one B200.
+"""A small, whole inference engine on one B200 for the dense Llama decoder and the Turudra decoder.
 
 From a model folder (config.json + model.safetensors) or a seeded random
 configuration to generated tokens: typed configuration and an architecture
