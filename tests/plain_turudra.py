@@ -97,10 +97,15 @@ def expert(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Te
     return y @ down.T
 
 
-def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], f: dict) -> torch.Tensor:
+def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], f: dict, chosen: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`chosen` [T, top] (optional): take these experts instead of the `top` largest logits (their weights are still the
+    softmax of their own logits): for comparing with a run whose rounding turned a near tie the other way."""
     E, top = f["router"]["experts"], f["router"]["top"]
     z = h @ w["router"].T
     best, idx = torch.topk(z, top, dim=-1)
+    if chosen is not None:
+        idx = chosen.to(torch.long)
+        best = torch.gather(z, 1, idx)
     wt = torch.softmax(best, dim=-1)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
@@ -129,8 +134,14 @@ def layer_order(cfg: dict) -> List[tuple]:
     return order + [(i, False) for i in range(b, L)]
 
 
-def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens, dtype=torch.float64, trace: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one whole sequence.  `trace` collects the residual stream after every layer run."""
+def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens, dtype=torch.float64, trace: Optional[list] = None,
+            routing: Optional[list] = None, round_inputs: bool = False) -> torch.Tensor:
+    """Logits [T, vocab] of one whole sequence.  `trace` collects the residual stream after every layer run.  `routing`:
+    the experts to take ([T, top] per layer run that has experts, in the order the layers run) instead of the router's choice.
+    `round_inputs`: every layer's normed input is rounded to bfloat16, the one rounding of a bfloat16 run that a layer with
+    a cancelling sum (the first tokens of the recurrence, where k . q may be near zero before the unit norm) amplifies
+    beyond all others; what is left between this and a bfloat16 run is rounding inside the layers."""
+    routing = list(routing) if routing is not None else None
     W = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
     x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)] * cfg["embedding"]["scale"]
@@ -140,6 +151,8 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens, dtype=torch.flo
         if first:
             x = torch.cat([x, x0], dim=-1) @ W["loop.in"].T
         h = rms_norm(x, W[f"l{i}.norm1"], eps)
+        if round_inputs:
+            h = h.to(torch.bfloat16).to(dtype)
         wm = sub(W, f"l{i}.mix.")
         if lay["type"] == "latent_attention":
             y = latent_attention(h, wm, lay["mixer"], eps)
@@ -148,7 +161,7 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens, dtype=torch.flo
         else:
             raise ValueError(lay["type"])
         if lay.get("mlp"):
-            y = y + moe(h, sub(W, f"l{i}.mlp."), lay["mlp"])
+            y = y + moe(h, sub(W, f"l{i}.mlp."), lay["mlp"], routing.pop(0) if routing else None)
         x = x + mult * y
         if trace is not None:
             trace.append(x.clone())
