@@ -112,7 +112,7 @@ class LatentAttention(Mixer):
                             ctx.max_pages, ctx.page_size, self.eps)
         o = ctx.buf("attn_out", (n, H * V), ctx.act_dtype)
         gate = proj if self.gated else None
-        if USE_MMA and kernels.latent_attention_mma_supported(ctx.act_dtype, D, R, C):
+        if USE_MMA and D > 0 and kernels.latent_attention_mma_supported(ctx.act_dtype, D, R, C):
             chunk, splits = ctx.once(("latent_splits", H), lambda: kernels.latent_attention_splits(n, H, ctx.max_kv_len))
             po = pm = None
             if splits > 1:
@@ -144,7 +144,10 @@ class LatentAttention(Mixer):
             counters["mma"] += 1
         else:
             ql = ctx.buf("latent_q", (n, H * C), torch.float32)
-            kernels.head_matmul(proj, 0, D + R, self.w_uk, False, ql, n, H, D, C)
+            if D > 0:
+                kernels.head_matmul(proj, 0, D + R, self.w_uk, False, ql, n, H, D, C)
+            else:
+                ql.zero_()                       # no plain query part: the scores come from the rotated parts alone
             ol = ctx.buf("latent_o", (n, H * C), torch.float32)
             kernels.latent_attention(ql, proj, D, D + R, ol, cache_ptr, page_stride, ctx.positions, ctx.tok_seg, bt, H, C, R,
                                      ctx.max_pages, ctx.page_size, self.scale)
