@@ -324,6 +324,139 @@ XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const in
 }
 
 // ---------------------------------------------------------------------------
+// RMSNorm of rows in the activation dtype (a projection's output that is normed before the next product):
+// out[t] = in[t] * rsqrt(mean(in[t]^2) + eps) * w, float32 arithmetic; rows may be strided.  One block per row.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+k_rmsnorm_act(const T* __restrict__ in, long long ld_in, const float* __restrict__ w, T* __restrict__ out, long long ld_out, int d, float eps) {
+    xr_pdl_launch();
+    __shared__ float scratch[33];
+    const T* src = in + (size_t)blockIdx.x * ld_in;
+    T* dst = out + (size_t)blockIdx.x * ld_out;
+    xr_pdl_wait();
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) { const float v = xr_to_f32<T>(src[i]); ss = fmaf(v, v, ss); }
+    ss = xr_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = xr_from_f32<T>(xr_to_f32<T>(src[i]) * inv * w[i]);
+}
+
+XR_EXPORT int xr_rmsnorm_act(const void* in, int dtype, long long ld_in, const float* w, void* out, long long ld_out, int n, int d, float eps,
+                             cudaStream_t stream) {
+    if (n < 1 || d < 1) return XR_ERR_ARG;
+    if (dtype == XR_F32) xr_launch((k_rmsnorm_act<float>), dim3(n), dim3(128), 0, stream, (const float*)in, ld_in, w, (float*)out, ld_out, d, eps);
+    else if (dtype == XR_BF16)
+        xr_launch((k_rmsnorm_act<__nv_bfloat16>), dim3(n), dim3(128), 0, stream, (const __nv_bfloat16*)in, ld_in, w, (__nv_bfloat16*)out, ld_out, d, eps);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Queries and keys with a norm per head before the rotation, and value heads of another size than the key heads.
+//
+// in: [n, ld_in] rows as one projection wrote them: Q heads [H][D], then K heads [K][D], then V heads [K][Vd].
+// Every Q and K head is divided by its root mean square (eps inside the root) and multiplied by a weight of D values
+// that all heads share (q_w, k_w; null: no norm), in float32; then the first rotary_dim elements are rotated, pair
+// (2j, 2j + 1) or (j, j + rotary_dim/2), by angle = position * freq[j] (a float64 product, cosine and sine rounded to
+// float32).  The attention kernels take one head size hd >= max(D, Vd) for keys and values: Q goes to
+// q_out [n, q_ld] (head h at h * hd), K and V to the token's cache rows, each head filled up to hd with zeros, which
+// change neither a score nor a sum.  One block per token, a warp per head.
+// ---------------------------------------------------------------------------
+struct QkNormStoreArgs {
+    const void* in;
+    long long ld_in;
+    void* q_out;
+    long long q_ld;
+    const int* positions;
+    const int* tok_seg;
+    const int* block_tables;
+    const double* freq;          // [rotary_dim / 2] or null when rotary_dim == 0
+    const float* q_w;
+    const float* k_w;
+    void* cache_k;               // null: this layer stores nothing
+    long long page_stride, v_offset;
+    int H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent;
+    float eps;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+k_qk_norm_rope_store(QkNormStoreArgs a) {
+    xr_pdl_launch();
+    extern __shared__ float qk_sm[];                   // [half] cosines, [half] sines, then D floats per warp
+    const int t = blockIdx.x, half = a.rotary_dim >> 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int pos = a.positions[t];
+    float* cs = qk_sm;
+    float* mine = qk_sm + 2 * half + (size_t)warp * a.D;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        double s, c;
+        sincos((double)pos * a.freq[j], &s, &c);
+        cs[j] = (float)c; cs[half + j] = (float)s;
+    }
+    T* kdst = nullptr;
+    if (a.cache_k != nullptr) {
+        const int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
+        kdst = (T*)a.cache_k + (size_t)page * a.page_stride + (size_t)(pos % a.page_size) * a.hd;
+    }
+    const size_t head_step = (size_t)a.page_size * a.hd;
+    __syncthreads();
+    xr_pdl_wait();
+    const T* row = (const T*)a.in + (size_t)t * a.ld_in;
+    const int heads = kdst ? a.H + a.K : a.H;
+    for (int head = warp; head < heads; head += nw) {
+        const T* src = row + (size_t)head * a.D;
+        const float* w = head < a.H ? a.q_w : a.k_w;
+        float ss = 0.f;
+        for (int e = lane; e < a.D; e += 32) { const float x = xr_to_f32<T>(src[e]); mine[e] = x; ss = fmaf(x, x, ss); }
+        ss = xr_warp_sum(ss);
+        const float inv = w != nullptr ? 1.0f / sqrtf(ss / (float)a.D + a.eps) : 1.0f;
+        __syncwarp();
+        T* dst = head < a.H ? (T*)a.q_out + (size_t)t * a.q_ld + (size_t)head * a.hd : kdst + (size_t)(head - a.H) * head_step;
+        for (int e = lane; e < a.hd; e += 32) {
+            float y = 0.f;
+            if (e < a.D) {
+                y = w != nullptr ? mine[e] * inv * w[e] : mine[e];
+                if (e < a.rotary_dim) {
+                    int j, other; bool first;
+                    if (a.adjacent) { j = e >> 1; first = !(e & 1); other = e ^ 1; }
+                    else { first = e < half; j = first ? e : e - half; other = first ? e + half : e - half; }
+                    const float z = w != nullptr ? mine[other] * inv * w[other] : mine[other];
+                    y = first ? y * cs[j] - z * cs[half + j] : y * cs[j] + z * cs[half + j];
+                }
+            }
+            dst[e] = xr_from_f32<T>(y);
+        }
+        __syncwarp();
+    }
+    if (kdst == nullptr) return;
+    T* vdst = kdst + a.v_offset;
+    const T* vsrc = row + (size_t)(a.H + a.K) * a.D;
+    for (int i = threadIdx.x; i < a.K * a.hd; i += blockDim.x) {
+        const int kvh = i / a.hd, e = i % a.hd;
+        vdst[(size_t)kvh * head_step + e] = e < a.Vd ? vsrc[(size_t)kvh * a.Vd + e] : xr_from_f32<T>(0.f);
+    }
+}
+
+XR_EXPORT int xr_qk_norm_rope_store(const void* in, int dtype, long long ld_in, void* q_out, long long q_ld, const int* positions,
+                                    const int* tok_seg, const int* block_tables, const double* freq, const float* q_w, const float* k_w,
+                                    void* cache_k, long long page_stride, long long v_offset, int n, int H, int K, int D, int Vd, int hd,
+                                    int rotary_dim, int max_pages, int page_size, int adjacent_pairs, float eps, cudaStream_t stream) {
+    if (n < 1 || H < 1 || K < 1 || D < 1 || Vd < 1 || hd < D || hd < Vd || rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) ||
+        page_size < 1 || (rotary_dim > 0 && freq == nullptr) || (q_w == nullptr) != (k_w == nullptr))
+        return XR_ERR_ARG;
+    QkNormStoreArgs a{in, ld_in, q_out, q_ld, positions, tok_seg, block_tables, freq, q_w, k_w, cache_k, page_stride, v_offset,
+                      H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent_pairs ? 1 : 0, eps};
+    const size_t smem = ((size_t)rotary_dim + 8 * (size_t)D) * sizeof(float);
+    if (smem > 48 * 1024) return XR_ERR_ARG;
+    if (dtype == XR_F32) xr_launch((k_qk_norm_rope_store<float>), dim3(n), dim3(256), smem, stream, a);
+    else if (dtype == XR_BF16) xr_launch((k_qk_norm_rope_store<__nv_bfloat16>), dim3(n), dim3(256), smem, stream, a);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
 // Activation of a feed-forward: gated, h = act(g) * u with g, u the two halves of each row of gu [n, 2F]
 // (src/model.c:4425-4452, `gated_act`); ungated, h = act(x) of x [n, F] (src/model.c:6380-6396).
 // act 1: SiLU, g / (1 + exp(-g)), 0 for g < -80 (src/model.c:4451-4452; the reference's kernel is

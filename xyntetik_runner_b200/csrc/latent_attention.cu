@@ -14,18 +14,18 @@
 #include <math.h>
 
 // ---------------------------------------------------------------------------------------------
-// Preparation, one block per token.  proj row t (activation dtype): the heads' queries [H][D + R] from column 0
-// and the down projection [C + R] from column `down_col`.
-//  * the last R values of every head's query are rotated in place (the first `rot_dims` of them: pair (i, i + rot_dims/2),
-//    angle = position * freq[i], cosine and sine from a float64 angle);
+// Preparation, one block per token.  q row t (activation dtype, ldq elements a row): the heads' queries [H][D + R];
+// down row t (ldd elements a row; null with a null cache): the down projection [C + R].
+//  * the last R values of every head's query are rotated in place: the first `rot_dims` of them, pair (i, i + rot_dims/2)
+//    or, with `adjacent`, pair (2i, 2i + 1); angle = position * freq[i], cosine and sine from a float64 angle;
 //  * c = down[:C] / sqrt(mean(down[:C]^2) + eps) * norm_w and r = rotate(down[C:]) go to the token's cache row.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
-k_latent_prep(T* __restrict__ proj, long long ldp, int down_col, const int* __restrict__ positions,
+k_latent_prep(T* __restrict__ q, long long ldq, const T* __restrict__ down_all, long long ldd, const int* __restrict__ positions,
               const int* __restrict__ tok_seg, const int* __restrict__ block_tables, const double* __restrict__ freq,
               const float* __restrict__ norm_w, T* __restrict__ cache, long long page_stride, int H, int D, int R, int C,
-              int rot_dims, int max_pages, int page_size, float eps) {
+              int rot_dims, int max_pages, int page_size, float eps, int adjacent) {
     xr_pdl_launch();
     __shared__ float scratch[33];
     extern __shared__ float cs[];            // cos [half], sin [half]
@@ -38,17 +38,19 @@ k_latent_prep(T* __restrict__ proj, long long ldp, int down_col, const int* __re
     }
     xr_pdl_wait();
     __syncthreads();
-    T* row = proj + (size_t)t * ldp;
+    // element indices of pair i
+    const int step = adjacent ? 2 : 1, apart = adjacent ? 1 : half;
+    T* row = q + (size_t)t * ldq;
     // queries
     for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
         int h = idx / half, i = idx % half;
         T* qr = row + (size_t)h * (D + R) + D;
-        float u = xr_to_f32<T>(qr[i]), v = xr_to_f32<T>(qr[i + half]);
-        qr[i] = xr_from_f32<T>(u * cs[i] - v * cs[half + i]);
-        qr[i + half] = xr_from_f32<T>(v * cs[i] + u * cs[half + i]);
+        float u = xr_to_f32<T>(qr[step * i]), v = xr_to_f32<T>(qr[step * i + apart]);
+        qr[step * i] = xr_from_f32<T>(u * cs[i] - v * cs[half + i]);
+        qr[step * i + apart] = xr_from_f32<T>(v * cs[i] + u * cs[half + i]);
     }
     if (cache == nullptr) return;
-    const T* down = row + down_col;
+    const T* down = down_all + (size_t)t * ldd;
     float ss = 0.f;
     for (int i = threadIdx.x; i < C; i += blockDim.x) { float v = xr_to_f32<T>(down[i]); ss += v * v; }
     ss = xr_block_sum(ss, scratch);
@@ -57,33 +59,39 @@ k_latent_prep(T* __restrict__ proj, long long ldp, int down_col, const int* __re
     T* dst = cache + (size_t)page * page_stride + (size_t)(pos % page_size) * (C + R);
     for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = xr_from_f32<T>(xr_to_f32<T>(down[i]) * inv * norm_w[i]);
     for (int i = threadIdx.x; i < R; i += blockDim.x) {
-        float out;
-        if (i < half) out = xr_to_f32<T>(down[C + i]) * cs[i] - xr_to_f32<T>(down[C + i + half]) * cs[half + i];
-        else if (i < rot_dims) out = xr_to_f32<T>(down[C + i]) * cs[i - half] + xr_to_f32<T>(down[C + i - half]) * cs[i];
-        else out = xr_to_f32<T>(down[C + i]);
+        float out = xr_to_f32<T>(down[C + i]);
+        if (i < rot_dims) {
+            int j, other; bool first;
+            if (adjacent) { j = i >> 1; first = !(i & 1); other = i ^ 1; }
+            else { first = i < half; j = first ? i : i - half; other = first ? i + half : i - half; }
+            const float z = xr_to_f32<T>(down[C + other]);
+            out = first ? out * cs[j] - z * cs[half + j] : out * cs[j] + z * cs[half + j];
+        }
         dst[C + i] = xr_from_f32<T>(out);
     }
 }
 
-XR_EXPORT int xr_latent_prep(void* proj, int dtype, long long ldp, int down_col, const int* positions, const int* tok_seg,
+XR_EXPORT int xr_latent_prep(void* q, int dtype, long long ldq, const void* down, long long ldd, const int* positions, const int* tok_seg,
                              const int* block_tables, const double* freq, const float* norm_w, void* cache,
                              long long page_stride, int n, int H, int D, int R, int C, int rot_dims, int max_pages,
-                             int page_size, float eps, cudaStream_t stream) {
+                             int page_size, float eps, int adjacent, cudaStream_t stream) {
     if (n < 1 || H < 1 || D < 0 || R < 0 || C < 1 || rot_dims < 0 || rot_dims > R || (rot_dims & 1) || page_size < 1) return XR_ERR_ARG;
+    if (cache != nullptr && (down == nullptr || norm_w == nullptr)) return XR_ERR_ARG;
     size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
     if (smem > 40000) return XR_ERR_ARG;
     if (dtype == XR_F32)
-        xr_launch((k_latent_prep<float>), dim3(n), dim3(256), smem, stream, (float*)proj, ldp, down_col, positions, tok_seg, block_tables,
-                  freq, norm_w, (float*)cache, page_stride, H, D, R, C, rot_dims, max_pages, page_size, eps);
+        xr_launch((k_latent_prep<float>), dim3(n), dim3(256), smem, stream, (float*)q, ldq, (const float*)down, ldd, positions, tok_seg, block_tables,
+                  freq, norm_w, (float*)cache, page_stride, H, D, R, C, rot_dims, max_pages, page_size, eps, adjacent ? 1 : 0);
     else if (dtype == XR_BF16)
-        xr_launch((k_latent_prep<__nv_bfloat16>), dim3(n), dim3(256), smem, stream, (__nv_bfloat16*)proj, ldp, down_col, positions, tok_seg,
-                  block_tables, freq, norm_w, (__nv_bfloat16*)cache, page_stride, H, D, R, C, rot_dims, max_pages, page_size, eps);
+        xr_launch((k_latent_prep<__nv_bfloat16>), dim3(n), dim3(256), smem, stream, (__nv_bfloat16*)q, ldq, (const __nv_bfloat16*)down, ldd, positions, tok_seg,
+                  block_tables, freq, norm_w, (__nv_bfloat16*)cache, page_stride, H, D, R, C, rot_dims, max_pages, page_size, eps, adjacent ? 1 : 0);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
 
 // ---------------------------------------------------------------------------------------------
-// A small matrix per head: out[t][h][j] = sum_k in[t][h][k] * W_h(k, j) (* sigmoid(gate[t][h])), float32 sums.
+// A small matrix per head: out[t][h][j] = sum_k in[t][h][k] * W_h(k, j) (* sigmoid(gate[t][h]), or, with `gate_each`,
+// * sigmoid(gate[t][h * J + j])), float32 sums.
 // in row t, head h starts at in + t * ld_in + h * head_in; W_h(k, j) = W[h * w_head + k * w_k + j * w_j]
 // (so both "W_h as stored" and its transpose are a choice of strides); out row t, head h at out + t * ld_out + h * J.
 // Tile: 64 tokens x 64 columns, 256 threads with 4 x 4 results each, 16 values of k a round.
@@ -92,7 +100,7 @@ template <typename TI, typename TW, typename TO, typename TG>
 __global__ void __launch_bounds__(256)
 k_head_matmul(const TI* __restrict__ in, long long ld_in, int head_in, const TW* __restrict__ W, long long w_head, long long w_k,
               long long w_j, TO* __restrict__ out, long long ld_out, const TG* __restrict__ gate, long long ld_gate,
-              int n, int Kd, int J) {
+              int n, int Kd, int J, int gate_each) {
     xr_pdl_launch();
     __shared__ float As[16][64 + 1], Ws[16][64 + 1];
     const int h = blockIdx.z, t0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
@@ -131,11 +139,13 @@ k_head_matmul(const TI* __restrict__ in, long long ld_in, int head_in, const TW*
         int t = t0 + ty + 16 * i;
         if (t >= n) continue;
         float g = 1.0f;
-        if (gate != nullptr) g = 1.0f / (1.0f + expf(-xr_to_f32<TG>(gate[(size_t)t * ld_gate + h])));
+        if (gate != nullptr && !gate_each) g = 1.0f / (1.0f + expf(-xr_to_f32<TG>(gate[(size_t)t * ld_gate + h])));
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             int c = j0 + tx + 16 * j;
-            if (c < J) out[(size_t)t * ld_out + (size_t)h * J + c] = xr_from_f32<TO>(acc[i][j] * g);
+            if (c >= J) continue;
+            if (gate != nullptr && gate_each) g = 1.0f / (1.0f + expf(-xr_to_f32<TG>(gate[(size_t)t * ld_gate + (size_t)h * J + c])));
+            out[(size_t)t * ld_out + (size_t)h * J + c] = xr_from_f32<TO>(acc[i][j] * g);
         }
     }
 }
@@ -143,12 +153,13 @@ k_head_matmul(const TI* __restrict__ in, long long ld_in, int head_in, const TW*
 // in_dtype / w_dtype / out_dtype: XR_F32 or XR_BF16; the gate (optional) has the dtype `gate_dtype`.
 XR_EXPORT int xr_head_matmul(const void* in, int in_dtype, long long ld_in, int head_in, const void* W, int w_dtype,
                              long long w_head, long long w_k, long long w_j, void* out, int out_dtype, long long ld_out,
-                             const void* gate, int gate_dtype, long long ld_gate, int n, int H, int Kd, int J, cudaStream_t stream) {
+                             const void* gate, int gate_dtype, long long ld_gate, int n, int H, int Kd, int J, int gate_each,
+                             cudaStream_t stream) {
     if (n < 1 || H < 1 || Kd < 1 || J < 1 || H > 65535) return XR_ERR_ARG;
     dim3 grid((n + 63) / 64, (J + 63) / 64, H);
     if (grid.y > 65535) return XR_ERR_ARG;
 #define HM(TI, TW, TO, TG) xr_launch((k_head_matmul<TI, TW, TO, TG>), grid, dim3(256), 0, stream, (const TI*)in, ld_in, head_in, (const TW*)W, \
-                                     w_head, w_k, w_j, (TO*)out, ld_out, (const TG*)gate, ld_gate, n, Kd, J)
+                                     w_head, w_k, w_j, (TO*)out, ld_out, (const TG*)gate, ld_gate, n, Kd, J, gate_each)
     typedef __nv_bfloat16 bf;
     const int key = in_dtype * 8 + w_dtype * 4 + out_dtype * 2 + (gate ? gate_dtype : 0);
     switch (key) {
@@ -169,7 +180,8 @@ XR_EXPORT int xr_head_matmul(const void* in, int in_dtype, long long ld_in, int 
 
 // ---------------------------------------------------------------------------------------------
 // Attention over the cached rows, one block per token, a warp per head (eight heads at a time).  Keys are taken in
-// tiles of 32 in ascending order from position 0, with a running maximum: a query's result depends on its position
+// tiles of 32 in ascending order from the first visible position (0, or position - window + 1 with a window of
+// `window` > 0 keys), with a running maximum: a query's result depends on its position
 // and the cached rows alone, not on how the step was cut or what else is in the batch.  The tile of 32 rows is
 // brought to shared memory once for the eight heads that share it.
 //   ql [n][H][C] float32: the queries in the latent space;  qr: the rotated query parts, head h of token t at
@@ -183,7 +195,7 @@ __global__ void __launch_bounds__(32 * LA_WARPS)
 k_latent_attention(const float* __restrict__ ql, const T* __restrict__ qr, long long ld_qr, int head_qr,
                    float* __restrict__ out, const T* __restrict__ cache, long long page_stride,
                    const int* __restrict__ positions, const int* __restrict__ tok_seg, const int* __restrict__ block_tables,
-                   int H, int C, int R, int max_pages, int page_size, float scale) {
+                   int H, int C, int R, int max_pages, int page_size, float scale, int window) {
     xr_pdl_launch();
     extern __shared__ float sm[];
     const int W = C + R, ldw = W | 1;                       // odd row stride: lanes that read one column of 32 rows hit 32 banks
@@ -193,6 +205,7 @@ k_latent_attention(const float* __restrict__ ql, const T* __restrict__ qr, long 
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int* bt = block_tables + (size_t)tok_seg[t] * max_pages;
+    const int kfirst = (window > 0 && pos >= window) ? pos - window + 1 : 0;     // the first key the token sees
     xr_pdl_wait();
     for (int h0 = 0; h0 < H; h0 += LA_WARPS) {
         const int h = h0 + warp;
@@ -208,7 +221,7 @@ k_latent_attention(const float* __restrict__ ql, const T* __restrict__ qr, long 
 #pragma unroll
         for (int i = 0; i < LA_MAX_ND; i++) acc[i] = 0.f;
         float m = -INFINITY, l = 0.f;
-        for (int k0 = 0; k0 <= pos; k0 += 32) {
+        for (int k0 = kfirst; k0 <= pos; k0 += 32) {
             const int cnt = min(32, pos - k0 + 1);
             __syncthreads();
             for (int j = warp; j < cnt; j += LA_WARPS) {
@@ -258,7 +271,7 @@ k_latent_attention(const float* __restrict__ ql, const T* __restrict__ qr, long 
 XR_EXPORT int xr_latent_attention(const float* ql, const void* qr, int dtype, long long ld_qr, int head_qr, float* out,
                                   const void* cache, long long page_stride, const int* positions, const int* tok_seg,
                                   const int* block_tables, int n, int H, int C, int R, int max_pages, int page_size,
-                                  float scale, cudaStream_t stream) {
+                                  float scale, int window, cudaStream_t stream) {
     if (n < 1 || H < 1 || C < 1 || C > 32 * LA_MAX_ND || R < 0 || page_size < 1) return XR_ERR_ARG;
     const size_t smem = (size_t)(32 + LA_WARPS) * ((C + R) | 1) * sizeof(float);
     if (smem > 220 * 1024) return XR_ERR_ARG;
@@ -267,13 +280,13 @@ XR_EXPORT int xr_latent_attention(const float* ql, const void* qr, int dtype, lo
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(k_latent_attention<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return XR_ERR_LAUNCH;
         xr_launch((k_latent_attention<float>), dim3(n), dim3(32 * LA_WARPS), smem, stream, ql, (const float*)qr, ld_qr, head_qr, out,
-                  (const float*)cache, page_stride, positions, tok_seg, block_tables, H, C, R, max_pages, page_size, scale);
+                  (const float*)cache, page_stride, positions, tok_seg, block_tables, H, C, R, max_pages, page_size, scale, window);
     } else if (dtype == XR_BF16) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(k_latent_attention<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return XR_ERR_LAUNCH;
         xr_launch((k_latent_attention<__nv_bfloat16>), dim3(n), dim3(32 * LA_WARPS), smem, stream, ql, (const __nv_bfloat16*)qr, ld_qr,
                   head_qr, out, (const __nv_bfloat16*)cache, page_stride, positions, tok_seg, block_tables, H, C, R, max_pages,
-                  page_size, scale);
+                  page_size, scale, window);
     } else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -291,7 +304,8 @@ XR_EXPORT int xr_latent_attention(const float* ql, const void* qr, int dtype, lo
 //   sums     O [16 x C] += P [16 x 32] V [32 x C], warp w owning columns w C/4 .. (w+1) C/4; V is the first C columns
 //            of the same rows, read through ldmatrix.trans.
 // grid = (tokens, tiles of 16 heads, splits).  With one split a CTA writes out = O / l; with more, split s takes keys
-// [s chunk, (s+1) chunk) and leaves (m, l, O) in scratch for k_latent_merge, which combines them per (token, head).
+// [first + s chunk, first + (s+1) chunk), first the first key the token sees (0, or position - window + 1), and leaves
+// (m, l, O) in scratch for k_latent_merge, which combines them per (token, head).
 // ---------------------------------------------------------------------------------------------
 #define LT_KT 32
 #define LT_NW 4
@@ -329,7 +343,7 @@ k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, long long ql_tok, l
                        float* __restrict__ part_o, float* __restrict__ part_ml,
                        const __nv_bfloat16* __restrict__ cache, long long page_stride, const int* __restrict__ positions,
                        const int* __restrict__ tok_seg, const int* __restrict__ block_tables, int H, int C, int R, int max_pages,
-                       int page_size, float scale, int chunk, int splits) {
+                       int page_size, float scale, int chunk, int splits, int window) {
     xr_pdl_launch();
     extern __shared__ __align__(16) uint8_t lt_sm[];
     const int W = C + R, Wp = (W + 15) / 16 * 16, rb = lt_row_bytes(Wp);
@@ -340,7 +354,8 @@ k_latent_attention_mma(const __nv_bfloat16* __restrict__ ql, long long ql_tok, l
     const int t = blockIdx.x, h0 = blockIdx.y * 16, split = blockIdx.z;
     const int pos = positions[t];
     const int* bt = block_tables + (size_t)tok_seg[t] * max_pages;
-    const int kbeg = split * chunk, kend = min(pos + 1, kbeg + chunk);       // keys [kbeg, kend)
+    const int kfirst = (window > 0 && pos >= window) ? pos - window + 1 : 0;     // the first key the token sees
+    const int kbeg = kfirst + split * chunk, kend = min(pos + 1, kbeg + chunk);  // keys [kbeg, kend)
     const int mt = gridDim.y;
     float* my_ml = part_ml + (((size_t)t * mt + blockIdx.y) * splits + split) * 32;
     float* my_o = part_o + (((size_t)t * mt + blockIdx.y) * splits + split) * 16 * (size_t)C;
@@ -571,7 +586,7 @@ XR_EXPORT int xr_latent_attention_mma_supported(int C, int R) {
 XR_EXPORT int xr_latent_attention_mma(const void* ql, long long ql_tok, long long ql_head, const void* qr, long long ld_qr, int head_qr,
                                       float* out, void* out_h, long long oh_tok, long long oh_head, float* part_o, float* part_ml, const void* cache, long long page_stride, const int* positions,
                                       const int* tok_seg, const int* block_tables, int n, int H, int C, int R, int max_pages,
-                                      int page_size, float scale, int chunk, int splits, cudaStream_t stream) {
+                                      int page_size, float scale, int chunk, int splits, int window, cudaStream_t stream) {
     if (n < 1 || H < 1 || !xr_latent_attention_mma_supported(C, R) || page_size < 1 || splits < 1 || chunk < LT_KT || chunk % LT_KT) return XR_ERR_ARG;
     if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return XR_ERR_ARG;
     if ((ql_tok | ql_head | oh_tok | oh_head) & 1) return XR_ERR_ARG;            // pairs of bfloat16 are read and written
@@ -586,7 +601,7 @@ XR_EXPORT int xr_latent_attention_mma(const void* ql, long long ql_tok, long lon
     const int mt = (H + 15) / 16;
     xr_launch(k_latent_attention_mma, dim3(n, mt, splits), dim3(32 * LT_NW), smem, stream, (const __nv_bfloat16*)ql, ql_tok, ql_head,
               (const __nv_bfloat16*)qr, ld_qr, head_qr, out, (__nv_bfloat16*)out_h, oh_tok, oh_head, part_o, part_ml, (const __nv_bfloat16*)cache, page_stride, positions, tok_seg, block_tables, H, C, R,
-              max_pages, page_size, scale, chunk, splits);
+              max_pages, page_size, scale, chunk, splits, window);
     if (splits > 1) {
         const long long warps = (long long)n * H;
         xr_launch(k_latent_merge, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, out, (__nv_bfloat16*)out_h, oh_tok, oh_head, n, H, C, mt, splits);
@@ -599,7 +614,8 @@ XR_EXPORT int xr_latent_attention_mma(const void* ql, long long ql_tok, long lon
 // Head-major copies around the per-head products on tensor cores (the grouped product wants the rows of one head
 // together, n_pad rows a head):
 //   gather:   out[h * n_pad + t][k] = in[t][h * head_in + k], k < Kd (rows t >= n: zeros)
-//   scatter:  y[t][h * J + j] = in[h * n_pad + t][j] * sigmoid(gate[t][h])     (in: the product's float32 sums, rounded once here)
+//   scatter:  y[t][h * J + j] = in[h * n_pad + t][j] * sigmoid(gate[t][h])     (in: the product's float32 sums, rounded once here;
+//             with `gate_each` the gate is gate[t][h * J + j])
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
 k_heads_gather(const __nv_bfloat16* __restrict__ in, long long ld_in, int head_in, __nv_bfloat16* __restrict__ out, int n, int n_pad, int Kd) {
@@ -617,14 +633,17 @@ k_heads_gather(const __nv_bfloat16* __restrict__ in, long long ld_in, int head_i
 
 __global__ void __launch_bounds__(128)
 k_heads_scatter_gate(const float* __restrict__ in, __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ gate,
-                     long long ld_gate, int n_pad, int H, int J) {
+                     long long ld_gate, int n_pad, int H, int J, int gate_each) {
     xr_pdl_launch();
     xr_pdl_wait();
     const int t = blockIdx.x, h = blockIdx.y;
-    const float g = gate != nullptr ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * ld_gate + h]))) : 1.0f;
+    float g = (gate != nullptr && !gate_each) ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * ld_gate + h]))) : 1.0f;
     const float* a = in + ((size_t)h * n_pad + t) * J;
     __nv_bfloat16* o = y + ((size_t)t * H + h) * J;
-    for (int j = threadIdx.x; j < J; j += blockDim.x) o[j] = __float2bfloat16_rn(a[j] * g);
+    for (int j = threadIdx.x; j < J; j += blockDim.x) {
+        if (gate != nullptr && gate_each) g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * ld_gate + (size_t)h * J + j])));
+        o[j] = __float2bfloat16_rn(a[j] * g);
+    }
 }
 
 XR_EXPORT int xr_heads_gather(const void* in, long long ld_in, int head_in, void* out, int n, int n_pad, int H, int Kd, cudaStream_t stream) {
@@ -634,9 +653,9 @@ XR_EXPORT int xr_heads_gather(const void* in, long long ld_in, int head_in, void
 }
 
 XR_EXPORT int xr_heads_scatter_gate(const void* in, void* y, const void* gate, long long ld_gate, int n, int n_pad, int H, int J,
-                                    cudaStream_t stream) {
+                                    int gate_each, cudaStream_t stream) {
     if (n < 1 || n_pad < n || H < 1 || H > 65535 || J < 1) return XR_ERR_ARG;
     xr_launch(k_heads_scatter_gate, dim3(n, H), dim3(128), 0, stream, (const float*)in, (__nv_bfloat16*)y, (const __nv_bfloat16*)gate,
-              ld_gate, n_pad, H, J);
+              ld_gate, n_pad, H, J, gate_each);
     return xr_launch_status();
 }

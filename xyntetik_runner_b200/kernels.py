@@ -72,13 +72,17 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_scaled_add": [_vp, _vp, _f, _i, _i, _vp],
         "xr_concat_cast": [_vp, _vp, _vp, _i, _i, _i, _vp],
         "xr_softcap": [_vp, _f, _ll, _vp],
-        "xr_latent_prep": [_vp, _i, _ll, _i, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
-        "xr_head_matmul": [_vp, _i, _ll, _i, _vp, _i, _ll, _ll, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _vp],
-        "xr_latent_attention": [_vp, _vp, _i, _ll, _i, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_latent_prep": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+        "xr_head_matmul": [_vp, _i, _ll, _i, _vp, _i, _ll, _ll, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _vp],
+        "xr_latent_attention": [_vp, _vp, _i, _ll, _i, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
         "xr_latent_attention_mma_supported": [_i, _i],
-        "xr_latent_attention_mma": [_vp, _ll, _ll, _vp, _ll, _i, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+        "xr_latent_attention_mma": [_vp, _ll, _ll, _vp, _ll, _i, _vp, _vp, _ll, _ll, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
         "xr_heads_gather": [_vp, _ll, _i, _vp, _i, _i, _i, _i, _vp],
-        "xr_heads_scatter_gate": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _vp],
+        "xr_heads_scatter_gate": [_vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _vp],
+        "xr_qk_norm_rope_store": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_rmsnorm_act": [_vp, _i, _ll, _vp, _vp, _ll, _i, _i, _f, _vp],
+        "xr_delta": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+        "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _f, _vp],
         "xr_mlstm": [_vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
         "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
         "xr_moe_plan": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -184,6 +188,37 @@ ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_SWISH_CLAMP = 0, 1, 2, 3
 # "swish_clamp" exists for gated products only and takes a `limit`: with g' = min(g, limit) and u' = u clamped to
 # [-limit, limit] the product stores g' sigmoid(1.702 g') (u' + 1).
 ACTIVATIONS = {"none": ACT_NONE, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH, "swish_clamp": ACT_SWISH_CLAMP}
+
+
+def rmsnorm_act(inp: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out[t] = inp[t] * rsqrt(mean(inp[t]^2) + eps) * w for rows in the activation dtype (rows may be strided); w float32."""
+    _dev(w)
+    n, d = inp.shape
+    assert out.shape == (n, d) and inp.dtype == out.dtype and inp.stride(1) == 1 and out.stride(1) == 1 and inp.is_cuda and out.is_cuda
+    assert w.dtype == torch.float32 and w.numel() == d
+    _check(lib().xr_rmsnorm_act(inp.data_ptr(), dtype_code(inp.dtype), inp.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), n, d,
+                                float(eps), _stream()), "rmsnorm_act")
+    _count()
+
+
+def qk_norm_rope_store(inp: torch.Tensor, q_out: torch.Tensor, positions, tok_seg, block_tables, freq: Optional[torch.Tensor],
+                       q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], cache_k_ptr: Optional[int], page_stride: int, v_offset: int,
+                       H: int, K: int, D: int, Vd: int, hd: int, rotary_dim: int, max_pages: int, page_size: int, adjacent: bool,
+                       eps: float) -> None:
+    """inp [n, >= (H + K) D + K Vd] (rows may be strided): Q heads, K heads (D each), V heads (Vd each).  Every Q and K head is
+    RMS-normed with the weight q_w / k_w (float32 [D], shared by the heads; None: no norm), its first `rotary_dim` elements rotated
+    (freq: float64 [rotary_dim / 2]); Q goes to q_out [n, *] (head h at column h * hd), K and V into the token's cache rows, every
+    head filled up to `hd` elements with zeros (cache_k_ptr None: nothing is stored)."""
+    _dev(positions, tok_seg, block_tables, freq, q_w, k_w)
+    n = inp.shape[0]
+    assert inp.stride(1) == 1 and q_out.stride(1) == 1 and inp.dtype == q_out.dtype and q_out.shape[0] == n and q_out.shape[1] >= H * hd
+    assert inp.shape[1] >= (H + K) * D + K * Vd and (freq is None or (freq.dtype == torch.float64 and freq.numel() >= rotary_dim // 2))
+    assert q_w is None or (q_w.dtype == torch.float32 and k_w.dtype == torch.float32 and q_w.numel() == D and k_w.numel() == D)
+    _check(lib().xr_qk_norm_rope_store(inp.data_ptr(), dtype_code(inp.dtype), inp.stride(0), q_out.data_ptr(), q_out.stride(0),
+                                       positions.data_ptr(), tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(freq), _ptr(q_w), _ptr(k_w),
+                                       cache_k_ptr, page_stride, v_offset, n, H, K, D, Vd, hd, rotary_dim, max_pages, page_size,
+                                       int(adjacent), float(eps), _stream()), "qk_norm_rope_store")
+    _count()
 
 
 def act_mul(gu: torch.Tensor, h: torch.Tensor, act: int = ACT_SILU, gated: bool = True, limit: float = 0.0) -> None:
@@ -636,24 +671,30 @@ def softcap(z: torch.Tensor, cap: float) -> None:
 
 # ---------------------------------------------------------------------------
 # Latent attention (csrc/latent_attention.cu)
-def latent_prep(proj: torch.Tensor, down_col: int, positions, tok_seg, block_tables, freq: Optional[torch.Tensor],
-                norm_w: torch.Tensor, cache_ptr: Optional[int], page_stride: int, H: int, D: int, R: int, C: int,
-                rot_dims: int, max_pages: int, page_size: int, eps: float) -> None:
-    """Rotate the rotated part of every head's query in `proj` in place; write the token's cache row
-    [normed latent (C) | rotated key part (R)] (cache_ptr None: write nothing).  freq: float64 [rot_dims / 2]."""
+def latent_prep(q: torch.Tensor, down: Optional[torch.Tensor], positions, tok_seg, block_tables, freq: Optional[torch.Tensor],
+                norm_w: Optional[torch.Tensor], cache_ptr: Optional[int], page_stride: int, H: int, D: int, R: int, C: int,
+                rot_dims: int, max_pages: int, page_size: int, eps: float, adjacent: bool = False) -> None:
+    """Rotate the rotated part of every head's query in `q` ([n, >= H (D + R)], rows may be strided) in place; from `down`
+    ([n, >= C + R], rows may be strided) write the token's cache row [normed latent (C) | rotated key part (R)] (cache_ptr
+    None: write nothing, `down` may be None).  freq: float64 [rot_dims / 2]; `adjacent`: pairs (2i, 2i + 1), else
+    (i, i + rot_dims / 2)."""
     _dev(positions, tok_seg, block_tables, freq, norm_w)
-    assert proj.stride(1) == 1 and proj.is_cuda
+    assert q.stride(1) == 1 and q.is_cuda and q.shape[1] >= H * (D + R)
     assert freq is None or freq.dtype == torch.float64
-    assert norm_w.dtype == torch.float32 and norm_w.numel() == C and proj.shape[1] >= down_col + C + R
-    _check(lib().xr_latent_prep(proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), down_col, positions.data_ptr(),
-                                tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(freq), norm_w.data_ptr(), cache_ptr, page_stride,
-                                proj.shape[0], H, D, R, C, rot_dims, max_pages, page_size, float(eps), _stream()), "latent_prep")
+    if cache_ptr is not None:
+        assert down is not None and down.stride(1) == 1 and down.dtype == q.dtype and down.shape[1] >= C + R
+        assert norm_w.dtype == torch.float32 and norm_w.numel() == C
+    _check(lib().xr_latent_prep(q.data_ptr(), dtype_code(q.dtype), q.stride(0), _ptr(down), 0 if down is None else down.stride(0),
+                                positions.data_ptr(), tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(freq), _ptr(norm_w), cache_ptr,
+                                page_stride, q.shape[0], H, D, R, C, rot_dims, max_pages, page_size, float(eps), int(adjacent), _stream()),
+           "latent_prep")
     _count()
 
 
 def head_matmul(inp: torch.Tensor, in_col: int, head_in: int, w: torch.Tensor, transposed: bool, out: torch.Tensor,
-                n: int, H: int, Kd: int, J: int, gate: Optional[torch.Tensor] = None, gate_col: int = 0) -> None:
-    """out[t, h, j] = sum_k inp[t, in_col + h * head_in + k] * W_h(k, j) (* sigmoid(gate[t, gate_col + h])), float32 sums.
+                n: int, H: int, Kd: int, J: int, gate: Optional[torch.Tensor] = None, gate_col: int = 0, gate_each: bool = False) -> None:
+    """out[t, h, j] = sum_k inp[t, in_col + h * head_in + k] * W_h(k, j) (* sigmoid(gate[t, gate_col + h]), or with `gate_each`
+    * sigmoid(gate[t, gate_col + h * J + j])), float32 sums.
     w [H * Kd, J] with W_h(k, j) = w[h * Kd + k, j], or `transposed`: w [H * J, Kd] with W_h(k, j) = w[h * J + j, k].
     out is [n, H * J] (any of the two dtypes)."""
     assert w.is_contiguous() and inp.stride(1) == 1 and out.is_contiguous() and out.shape == (n, H * J)
@@ -664,14 +705,15 @@ def head_matmul(inp: torch.Tensor, in_col: int, head_in: int, w: torch.Tensor, t
     _check(lib().xr_head_matmul(inp.data_ptr() + in_col * es, dtype_code(inp.dtype), inp.stride(0), head_in, w.data_ptr(),
                                 dtype_code(w.dtype), w_head, w_k, w_j, out.data_ptr(), dtype_code(out.dtype), out.stride(0),
                                 gptr, 0 if gate is None else dtype_code(gate.dtype), 0 if gate is None else gate.stride(0),
-                                n, H, Kd, J, _stream()), "head_matmul")
+                                n, H, Kd, J, int(gate_each), _stream()), "head_matmul")
     _count()
 
 
 def latent_attention(ql: torch.Tensor, proj: torch.Tensor, qr_col: int, head_qr: int, out: torch.Tensor, cache_ptr: int,
                      page_stride: int, positions, tok_seg, block_tables, H: int, C: int, R: int, max_pages: int,
-                     page_size: int, scale: float) -> None:
-    """Causal softmax attention of every token over its request's cached rows [latent (C) | rotated key part (R)]:
+                     page_size: int, scale: float, window: int = 0) -> None:
+    """Causal softmax attention of every token over its request's cached rows [latent (C) | rotated key part (R)] (all of
+    them, or the last `window` > 0 up to the token itself):
     ql [n, H * C] float32 (queries in the latent space), rotated query parts in `proj` (head h at column
     qr_col + h * head_qr), out [n, H * C] float32 = sum_j a_j latent_j."""
     _dev(ql, out, positions, tok_seg, block_tables)
@@ -680,7 +722,7 @@ def latent_attention(ql: torch.Tensor, proj: torch.Tensor, qr_col: int, head_qr:
     _check(lib().xr_latent_attention(ql.data_ptr(), proj.data_ptr() + qr_col * proj.element_size(), dtype_code(proj.dtype),
                                      proj.stride(0), head_qr, out.data_ptr(), cache_ptr, page_stride, positions.data_ptr(),
                                      tok_seg.data_ptr(), block_tables.data_ptr(), n, H, C, R, max_pages, page_size, float(scale),
-                                     _stream()), "latent_attention")
+                                     int(window), _stream()), "latent_attention")
     _count()
 
 
@@ -704,12 +746,13 @@ def latent_attention_splits(n: int, H: int, max_kv_len: int, sms: int = 148) -> 
 def latent_attention_mma(ql: torch.Tensor, proj: torch.Tensor, qr_col: int, head_qr: int, out: torch.Tensor,
                          part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], cache_ptr: int, page_stride: int,
                          positions, tok_seg, block_tables, H: int, C: int, R: int, max_pages: int, page_size: int, scale: float,
-                         chunk: int, splits: int, n_pad: Optional[int] = None) -> None:
+                         chunk: int, splits: int, n_pad: Optional[int] = None, window: int = 0) -> None:
     """``latent_attention`` on tensor cores, bfloat16 queries and cache.  Token-major (n_pad None): ql [n, H * C], out
     [n, H * C] float32.  Head-major (n_pad given): ql and out are [H * n_pad, C] bfloat16, head h of token t in row
     h * n_pad + t (the layout of the grouped per-head products).  With `splits` > 1 every range of `chunk` keys is a
     CTA of its own and part_o [n * ceil(H/16) * splits * 16 * C] and part_ml [n * ceil(H/16) * splits * 32] (float32)
-    carry their results to the kernel that merges them."""
+    carry their results to the kernel that merges them; the ranges start at the first key a token sees (`window` > 0: the
+    last `window` keys up to the token itself)."""
     _dev(ql, out, positions, tok_seg, block_tables, part_o, part_ml)
     n = positions.numel()
     mt = -(-H // 16)
@@ -725,7 +768,7 @@ def latent_attention_mma(ql: torch.Tensor, proj: torch.Tensor, qr_col: int, head
     _check(lib().xr_latent_attention_mma(ql.data_ptr(), q_tok, q_head, proj.data_ptr() + qr_col * 2, proj.stride(0), head_qr, o32, o16,
                                          o_tok, o_head, _ptr(part_o), _ptr(part_ml), cache_ptr, page_stride, positions.data_ptr(),
                                          tok_seg.data_ptr(), block_tables.data_ptr(), n, H, C, R, max_pages, page_size, float(scale),
-                                         chunk, splits, _stream()), "latent_attention_mma")
+                                         chunk, splits, int(window), _stream()), "latent_attention_mma")
     _count(2 if splits > 1 else 1)
 
 
@@ -737,12 +780,14 @@ def heads_gather(inp: torch.Tensor, in_col: int, head_in: int, out: torch.Tensor
     _count()
 
 
-def heads_scatter_gate(inp: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], gate_col: int, n: int, n_pad: int, H: int, J: int) -> None:
-    """y[t, h * J + j] = inp[h * n_pad + t, j] * sigmoid(gate[t, gate_col + h]) (inp float32, y and gate bfloat16)."""
+def heads_scatter_gate(inp: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], gate_col: int, n: int, n_pad: int, H: int, J: int,
+                       gate_each: bool = False) -> None:
+    """y[t, h * J + j] = inp[h * n_pad + t, j] * sigmoid(gate[t, gate_col + h]) (inp float32, y and gate bfloat16); with
+    `gate_each` the gate is gate[t, gate_col + h * J + j]."""
     _dev(inp, y)
     assert inp.dtype == torch.float32 and y.dtype == torch.bfloat16 and inp.shape == (H * n_pad, J) and y.shape == (n, H * J)
     gptr = None if gate is None else gate.data_ptr() + 2 * gate_col
-    _check(lib().xr_heads_scatter_gate(inp.data_ptr(), y.data_ptr(), gptr, 0 if gate is None else gate.stride(0), n, n_pad, H, J, _stream()),
+    _check(lib().xr_heads_scatter_gate(inp.data_ptr(), y.data_ptr(), gptr, 0 if gate is None else gate.stride(0), n, n_pad, H, J, int(gate_each), _stream()),
            "heads_scatter_gate")
     _count()
 
@@ -769,6 +814,50 @@ def mlstm(proj: torch.Tensor, cols, gates: torch.Tensor, state: torch.Tensor, co
                           seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), n, n_seg, H, D, V, float(cap), float(eps),
                           _stream()), "mlstm")
     _count(3)
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, w: torch.Tensor, y: torch.Tensor, H: int, V: int, eps: float,
+                   per_head_weight: bool = False, silu: bool = False) -> None:
+    """y [n, H V] = o / rms(o per head) * w * act(gate[:, gate_col + h V + i]): o float32 [n, H V]; gate and y in the activation
+    dtype; w float32, V values for all heads or (`per_head_weight`) H V; act the sigmoid, or SiLU with `silu`."""
+    _dev(o, w, y)
+    n = o.shape[0]
+    assert o.dtype == torch.float32 and o.shape == (n, H * V) and y.shape == (n, H * V) and gate.dtype == y.dtype and gate.stride(1) == 1
+    assert w.dtype == torch.float32 and w.numel() == (H * V if per_head_weight else V) and gate.shape[1] >= gate_col + H * V
+    _check(lib().xr_head_norm_gate(o.data_ptr(), gate.data_ptr() + gate_col * gate.element_size(), dtype_code(gate.dtype), gate.stride(0),
+                                   w.data_ptr(), V if per_head_weight else 0, int(silu), y.data_ptr(), n, H, V, float(eps), _stream()),
+           "head_norm_gate")
+    _count()
+
+
+# ---------------------------------------------------------------------------
+# Gated delta rule (csrc/delta.cu)
+def delta_state_floats(H: int, G: int, D: int, V: int, taps: int) -> int:
+    """float32 values per request slot: S [H][V][D], then the last taps - 1 inputs of the convolutions' 2 G D + H V channels."""
+    return H * V * D + (taps - 1) * (2 * G * D + H * V)
+
+
+def delta(proj: torch.Tensor, conv_w: torch.Tensor, gates: torch.Tensor, neg_a: torch.Tensor, dt_bias: torch.Tensor,
+          state: torch.Tensor, qkv: torch.Tensor, coef: torch.Tensor, o: torch.Tensor, tok_seg, seg_start, seg_len, seg_slot,
+          n_seg: int, H: int, G: int, D: int, V: int, taps: int) -> None:
+    """The gated delta rule over the step's tokens, request by request, from and into `state` [slots, delta_state_floats].
+    proj [n, >= CH] (rows may be strided): the convolutions' channels q [G D], k [G D], v [H V] from column 0; conv_w [CH, taps]
+    float32; gates [n, 2H] float32 (pre-activations of beta, then of the decay); neg_a = -exp(A_log) and dt_bias [H] float32;
+    qkv [n, CH] and coef [n, 2H] float32 scratch; o [n, H V] float32 receives the read-outs."""
+    _dev(conv_w, gates, neg_a, dt_bias, state, qkv, coef, o, tok_seg, seg_start, seg_len, seg_slot)
+    n = proj.shape[0]
+    CH = 2 * G * D + H * V
+    assert proj.stride(1) == 1 and proj.shape[1] >= CH and conv_w.shape == (CH, taps) and conv_w.dtype == torch.float32
+    assert gates.dtype == torch.float32 and gates.shape == (n, 2 * H) and state.dtype == torch.float32 and state.dim() == 2
+    assert state.shape[1] >= delta_state_floats(H, G, D, V, taps) and neg_a.numel() == H and dt_bias.numel() == H
+    assert neg_a.dtype == torch.float32 and dt_bias.dtype == torch.float32
+    assert qkv.shape == (n, CH) and qkv.dtype == torch.float32 and coef.numel() >= 2 * n * H and coef.dtype == torch.float32
+    assert o.shape == (n, H * V) and o.dtype == torch.float32
+    _check(lib().xr_delta(proj.data_ptr(), dtype_code(proj.dtype), proj.stride(0), conv_w.data_ptr(), gates.data_ptr(), neg_a.data_ptr(),
+                          dt_bias.data_ptr(), state.data_ptr(), state.stride(0), qkv.data_ptr(), coef.data_ptr(), o.data_ptr(),
+                          tok_seg.data_ptr(), seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), n, n_seg, H, G, D, V, taps,
+                          _stream()), "delta")
+    _count(3 if taps > 1 else 2)
 
 
 # ---------------------------------------------------------------------------

@@ -3,6 +3,7 @@ from .base import (Block, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncodi
                    register_block, register_feed_forward, register_mixer, register_norm, register_position)
 from .attention import GQAAttention
 from .block import ParallelBlock, PreNormBlock
+from .delta import GatedDelta
 from .embedding import Embedding, Head
 from .feed_forward import GatedFeedForward, MLP, SwiGLU
 from .latent_attention import LatentAttention

@@ -7,6 +7,13 @@ head h / (H/K); scores are (q . k) * scale over the keys t0..p, softmax in
 float32, weighted sum of V (src/model.c:3548-3589); then x += Wo o (+bo)
 (src/model.c:6338, 6350-6352).  Heads, kv heads, head size, scale, window and
 position encoding are all arguments.
+
+Options: `qk_norm` puts an RMSNorm over every query and key head (one weight of head_dim values for all query heads,
+one for all key heads, eps `norm_eps`) between the projection and the rotation; `value_dim` gives the value heads
+another size than the query/key heads.  With either, the projection's rows go through one kernel that norms, rotates
+(angles from float64 products) and stores; keys and values are then cached with one head size, the larger of the two
+rounded up to a multiple of 16 and filled with zeros, which changes no score and no sum, and the output product's
+matrix gets zero columns to match.
 """
 from __future__ import annotations
 
@@ -14,6 +21,7 @@ import math
 import os
 from typing import Optional
 
+import numpy as np
 import torch
 
 from .. import kernels
@@ -35,34 +43,52 @@ class GQAAttention(Mixer):
     graph_safe = True
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, position: PositionEncoding,
                  prefix: str, bias: bool = False, window: Optional[int] = None, scale: Optional[float] = None,
-                 q: str = "q_proj", k: str = "k_proj", v: str = "v_proj", o: str = "o_proj"):
+                 q: str = "q_proj", k: str = "k_proj", v: str = "v_proj", o: str = "o_proj", weight_suffix: str = ".weight",
+                 value_dim: Optional[int] = None, qk_norm: bool = False, norm_eps: float = 1e-6,
+                 q_norm: str = "q.norm", k_norm: str = "k.norm"):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
-        if not (1 <= head_dim <= 256):
-            raise ValueError(f"head_dim {head_dim}: the attention kernels take head sizes up to 256")
-        self.width, self.H, self.K, self.hd = width, heads, kv_heads, head_dim
+        self.D = head_dim                                      # query/key elements per head
+        self.Vd = head_dim if value_dim is None else value_dim  # value elements per head
+        # the general path: a norm per head, or values of another size than keys
+        self.general = bool(qk_norm) or self.Vd != self.D
+        if self.general and bias:
+            raise ValueError(f"{prefix}: biases are not combined with qk_norm or value_dim")
+        # head size of the cache and of the attention kernels
+        hd = -(-max(self.D, self.Vd) // 16) * 16 if self.general else head_dim
+        if not (1 <= hd <= 256):
+            raise ValueError(f"head_dim {hd}: the attention kernels take head sizes up to 256")
+        self.width, self.H, self.K, self.hd = width, heads, kv_heads, hd
         self.position, self.prefix, self.bias, self.window = position, prefix, bias, window
         self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)   # src/model.h:464-467
         self.proj = (q, k, v, o)
+        self.suffix = weight_suffix
+        self.qk_norm, self.norm_eps = bool(qk_norm), float(norm_eps)
+        self.norm_names = (prefix + q_norm, prefix + k_norm)
         self.qkv = self.out = None
         self.rot = None
+        self.q_norm_w = self.k_norm_w = self.freq64 = None
 
     def kv_need(self):
         return KVNeed(self.K, self.hd, self.window)
 
     def tensors(self):
         q, k, v, o = (self.prefix + n for n in self.proj)
-        qd, kd = self.H * self.hd, self.K * self.hd
-        t = {q + ".weight": TensorSpec((qd, self.width)), k + ".weight": TensorSpec((kd, self.width)),
-             v + ".weight": TensorSpec((kd, self.width)), o + ".weight": TensorSpec((self.width, qd))}
+        sfx = self.suffix
+        qd, kd, vd = self.H * self.D, self.K * self.D, self.K * self.Vd
+        t = {q + sfx: TensorSpec((qd, self.width)), k + sfx: TensorSpec((kd, self.width)),
+             v + sfx: TensorSpec((vd, self.width)), o + sfx: TensorSpec((self.width, self.H * self.Vd))}
         if self.bias:
             t.update({q + ".bias": TensorSpec((qd,), "vector", "zeros"), k + ".bias": TensorSpec((kd,), "vector", "zeros"),
                       v + ".bias": TensorSpec((kd,), "vector", "zeros"), o + ".bias": TensorSpec((self.width,), "vector", "zeros")})
+        if self.qk_norm:
+            t.update({n: TensorSpec((self.D,), "vector", "ones_jitter") for n in self.norm_names})
         return t
 
     def bind(self, tensors, rt):
         q, k, v, o = (self.prefix + n for n in self.proj)
-        ws = [tensors.pop(n + ".weight") for n in (q, k, v)]
+        sfx = self.suffix
+        ws = [tensors.pop(n + sfx) for n in (q, k, v)]
         if len({w.dtype for w in ws}) > 1:
             ws = [w.to(torch.float32) for w in ws]
         bias = obias = None
@@ -71,21 +97,36 @@ class GQAAttention(Mixer):
             obias = tensors[o + ".bias"]
         self.qkv = Linear(torch.cat(ws, dim=0), bias).prepare(rt)
         del ws
-        self.out = Linear(tensors[o + ".weight"], obias).prepare(rt)
+        wo = tensors[o + sfx]
+        if self.hd != self.Vd:
+            # the attention's output rows hold hd values a head, of which the first Vd are the head's: zero columns for the rest
+            wide = torch.zeros((self.width, self.H, self.hd), dtype=wo.dtype, device=wo.device)
+            wide[:, :, :self.Vd] = wo.view(self.width, self.H, self.Vd)
+            wo = wide.view(self.width, self.H * self.hd)
+        self.out = Linear(wo, obias).prepare(rt)
+        self._out_bytes = self.width * self.H * self.Vd * wo.element_size()
+        if self.qk_norm:
+            self.q_norm_w, self.k_norm_w = (tensors[n].to(torch.float32).contiguous() for n in self.norm_names)
         self.position.prepare(rt)
         try:
             rot = self.position.rotary()
         except NotImplementedError as e:
             raise ValueError(f"{self.prefix}: this mixer takes position encodings that rotate query and key pairs, or "
                              f"none ({e}); another kind needs a mixer of its own") from None
-        if rot is not None and rot.rotary_dim > self.hd:
-            raise ValueError(f"{self.prefix}: rotary_dim {rot.rotary_dim} exceeds head_dim {self.hd}")
+        if rot is not None and rot.rotary_dim > self.D:
+            raise ValueError(f"{self.prefix}: rotary_dim {rot.rotary_dim} exceeds head_dim {self.D}")
         # (rotary_dim, inv_freq, adjacent pairs, mscale) as the rotation kernels take them
         self.rot = (0, None, False, 1.0) if rot is None or rot.rotary_dim == 0 else \
             (rot.rotary_dim, rot.inv_freq, rot.pairing == "adjacent", rot.mscale)
+        if self.general and self.rot[0]:
+            if self.rot[3] != 1.0:
+                raise ValueError(f"{self.prefix}: scaled cosines and sines are not combined with qk_norm or value_dim")
+            f64 = getattr(self.position, "inv_freq64_host", None)
+            f64 = rot.inv_freq.double().cpu().numpy() if f64 is None else f64
+            self.freq64 = torch.from_numpy(np.ascontiguousarray(f64, dtype=np.float64)).to(rt.device)
 
     def weight_bytes(self):
-        return self.qkv.nbytes() + self.out.nbytes()
+        return self.qkv.nbytes() + self._out_bytes
 
     @staticmethod
     def _portions(ctx, G):
@@ -100,22 +141,31 @@ class GQAAttention(Mixer):
         n = h.shape[0]
         qkv_dim = (self.H + 2 * self.K) * self.hd
         qkv = ctx.buf("attn_qkv", (n, qkv_dim), ctx.act_dtype)
-        pend = self.qkv.forward(h, qkv, defer=True)
         k_ptr, page_stride, v_offset = ctx.cache_layer(lay)
         bt = ctx.block_tables[lay.group]
         store_ptr = k_ptr if lay.writes_cache else None
         rot_dim, rot_freq, adjacent, mscale = self.rot
-        if pend is not None and lay.writes_cache:
-            # the product was split along K: its finish, the rotation and the page store are one kernel
-            kernels.finish_rope_store(pend.partial, pend.splits, pend.bias, qkv, ctx.positions, ctx.tok_seg, bt,
-                                      rot_freq, store_ptr, page_stride, v_offset, self.H, self.K, self.hd,
-                                      rot_dim, ctx.max_pages, ctx.page_size, adjacent, mscale)
-            pend.release()
+        if self.general:
+            # the projection's rows [Q | K | V] in their own sizes; norm, rotation and store in one kernel, Q into `qkv`
+            cols = (self.H + self.K) * self.D + self.K * self.Vd
+            proj = ctx.buf("attn_proj", (n, -(-cols // 8) * 8), ctx.act_dtype)[:, :cols]
+            self.qkv.forward(h, proj)
+            kernels.qk_norm_rope_store(proj, qkv, ctx.positions, ctx.tok_seg, bt, self.freq64, self.q_norm_w, self.k_norm_w, store_ptr,
+                                       page_stride, v_offset, self.H, self.K, self.D, self.Vd, self.hd, rot_dim, ctx.max_pages,
+                                       ctx.page_size, adjacent, self.norm_eps)
         else:
-            if pend is not None:
-                pend.finish()
-            kernels.rope_store(qkv, ctx.positions, ctx.tok_seg, bt, rot_freq, store_ptr, page_stride,
-                               v_offset, self.H, self.K, self.hd, rot_dim, ctx.max_pages, ctx.page_size, adjacent, mscale)
+            pend = self.qkv.forward(h, qkv, defer=True)
+            if pend is not None and lay.writes_cache:
+                # the product was split along K: its finish, the rotation and the page store are one kernel
+                kernels.finish_rope_store(pend.partial, pend.splits, pend.bias, qkv, ctx.positions, ctx.tok_seg, bt,
+                                          rot_freq, store_ptr, page_stride, v_offset, self.H, self.K, self.hd,
+                                          rot_dim, ctx.max_pages, ctx.page_size, adjacent, mscale)
+                pend.release()
+            else:
+                if pend is not None:
+                    pend.finish()
+                kernels.rope_store(qkv, ctx.positions, ctx.tok_seg, bt, rot_freq, store_ptr, page_stride,
+                                   v_offset, self.H, self.K, self.hd, rot_dim, ctx.max_pages, ctx.page_size, adjacent, mscale)
         o = ctx.buf("attn_out", (n, self.H * self.hd), ctx.act_dtype)
         # Q is read in place from the fused rows (row stride = qkv_dim)
         G = self.H // self.K

@@ -9,11 +9,14 @@ from .base import Block, FeedForward, Mixer, Norm, register_block
 
 
 class PreNormBlock(Block):
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm, feed_forward: FeedForward):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm = None, feed_forward: FeedForward = None):
+        """`feed_forward` None: a layer of the mixer alone (no second norm either)."""
+        if (ff_norm is None) != (feed_forward is None):
+            raise ValueError("a feed-forward and its norm come together")
         self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = mixer_norm, mixer, ff_norm, feed_forward
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward)
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None)
 
     @property
     def graph_safe(self):
@@ -38,8 +41,9 @@ class PreNormBlock(Block):
         h = ctx.buf("block_normed", (x.shape[0], x.shape[1]), ctx.act_dtype)
         self.mixer_norm.forward(ctx, x, h)
         self.mixer.forward(ctx, h, x, lay)
-        self.ff_norm.forward(ctx, x, h)
-        self.feed_forward.forward(ctx, h, x)
+        if self.feed_forward is not None:
+            self.ff_norm.forward(ctx, x, h)
+            self.feed_forward.forward(ctx, h, x)
 
 
 register_block("prenorm", PreNormBlock)

@@ -1,4 +1,5 @@
-"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, computed in float32 (src/model.c:3386-3392)."""
+"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, computed in float32 (src/model.c:3386-3392).  With `one_plus` the
+stored weight is an offset from one: the factor is 1 + w."""
 from __future__ import annotations
 
 import torch
@@ -10,16 +11,18 @@ from .base import Norm, register_norm
 
 class RMSNorm(Norm):
     graph_safe = True
-    def __init__(self, width: int, eps: float, name: str):
-        self.width, self.eps, self.name = width, float(eps), name
+    def __init__(self, width: int, eps: float, name: str, one_plus: bool = False):
+        self.width, self.eps, self.name, self.one_plus = width, float(eps), name, bool(one_plus)
         self.weight = None
 
     def tensors(self):
-        return {self.name: TensorSpec((self.width,), kind="vector", init="ones_jitter")}
+        return {self.name: TensorSpec((self.width,), kind="vector", init="zeros_jitter" if self.one_plus else "ones_jitter")}
 
     def bind(self, tensors, rt):
         # norm weights are used in float32 whatever they were stored in (src/model.c:2830-2831)
         self.weight = tensors[self.name].to(torch.float32).contiguous()
+        if self.one_plus:
+            self.weight = (1.0 + self.weight).contiguous()      # the factor itself, made once in float32
 
     def weight_bytes(self):
         return self.width * 4

@@ -59,10 +59,13 @@ class Rope(PositionEncoding):
             inv = (inv / div).astype(np.float32)
         self.inv_freq_host = inv
         self.inv_freq = None
-        # the same frequencies in float64, for kernels that take the angle in float64 (unscaled frequencies only)
+        # the same frequencies in float64, for kernels that take the angle in float64 (unscaled or linearly scaled frequencies only)
         self.inv_freq64_host = None
-        if scaling is None and half:
+        linear = scaling is not None and getattr(scaling, "rope_type", "llama3") == "linear"
+        if (scaling is None or linear) and half:
             self.inv_freq64_host = np.power(float(theta), -2.0 * np.arange(half, dtype=np.float64) / float(self.rotary_dim))
+            if linear:
+                self.inv_freq64_host = self.inv_freq64_host / float(scaling.factor)
 
     def prepare(self, rt):
         self.inv_freq = torch.from_numpy(self.inv_freq_host.copy()).to(rt.device)

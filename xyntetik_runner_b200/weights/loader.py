@@ -29,7 +29,8 @@ from .safetensors_io import SafetensorsFile, open_model_files, read_weight_map
 class TensorSpec:
     shape: Tuple[int, ...]
     kind: str = "matrix"          # "matrix" | "vector" | "table" (integers)
-    init: str = "normal"          # random mode: "normal" | "ones" | "ones_jitter" | "zeros"
+    init: str = "normal"          # random mode: "normal" | "ones" | "ones_jitter" | "zeros" | "zeros_jitter"
+    optional: bool = False        # a source may lack it (the model then never reads it); random sources leave it out
 
 
 class WeightsError(ValueError):
@@ -117,7 +118,7 @@ class RandomSource(TensorSource):
         return torch.int32 if spec.kind == "table" else self.dtype
 
     def listing(self):
-        return {n: (self.dtype_of(s), tuple(s.shape)) for n, s in self.specs.items()}
+        return {n: (self.dtype_of(s), tuple(s.shape)) for n, s in self.specs.items() if not s.optional}
 
     def law(self, spec: TensorSpec):
         """(mean, std) of a spec's values, or a constant."""
@@ -127,6 +128,8 @@ class RandomSource(TensorSource):
             return 1.0
         if spec.init == "ones_jitter":
             return (1.0, self.jitter) if self.jitter > 0 else 1.0
+        if spec.init == "zeros_jitter":
+            return (0.0, self.jitter) if self.jitter > 0 else 0.0
         return (0.0, self.std)
 
     def fetch(self, name, device):
@@ -153,7 +156,7 @@ def load_tensors(expected: Mapping[str, TensorSpec], source: TensorSource,
                  device: torch.device) -> Dict[str, torch.Tensor]:
     """Fetch exactly the expected tensors; raise one WeightsError for every mismatch."""
     have = source.listing()
-    missing = [n for n in expected if n not in have]
+    missing = [n for n, spec in expected.items() if n not in have and not spec.optional]
     unexpected = sorted(n for n in have if n not in expected)
     wrong, bad = [], []
     for n, spec in expected.items():
@@ -171,6 +174,8 @@ def load_tensors(expected: Mapping[str, TensorSpec], source: TensorSource,
         raise WeightsError(source.where, missing, unexpected, wrong, bad)
     out: Dict[str, torch.Tensor] = {}
     for n, spec in expected.items():
+        if n not in have:
+            continue                              # (optional, and the source lacks it)
         t = source.fetch(n, device)
         if spec.kind == "table":
             t = t.to(torch.int32)
@@ -189,9 +194,9 @@ def write_model_folder(path: str, config_dict: dict, specs: Mapping[str, TensorS
     from .safetensors_io import write_safetensors
     os.makedirs(path, exist_ok=True)
     src = RandomSource(specs, seed, dtype, std=std, norm_jitter=norm_jitter, gen_device=gen_device)
-    layout = [(n, src.dtype_of(s), tuple(s.shape)) for n, s in specs.items()]
+    layout = [(n, src.dtype_of(s), tuple(s.shape)) for n, s in specs.items() if not s.optional]
     cpu = torch.device("cpu")
     write_safetensors(os.path.join(path, "model.safetensors"),
-                      ((n, src.fetch(n, cpu)) for n in specs), metadata={"format": "pt"}, layout=layout)
+                      ((n, src.fetch(n, cpu)) for n, s in specs.items() if not s.optional), metadata={"format": "pt"}, layout=layout)
     with open(os.path.join(path, "config.json"), "w", encoding="utf-8") as f:
         json.dump(config_dict, f, indent=1)
