@@ -91,7 +91,7 @@ def short_conv(z: torch.Tensor, taps: torch.Tensor) -> torch.Tensor:
     """z [T, C], taps [C, K]: out[t, c] = sum_j taps[c, K-1-j] z[t-j, c], zeros before the start."""
     T, K = z.shape[0], taps.shape[1]
     out = torch.zeros_like(z)
-    for j in range(K):
+    for j in range(min(K, T)):
         out[j:] += z[:T - j] * taps[:, K - 1 - j]
     return out
 

@@ -105,10 +105,12 @@ def run_plain(args) -> int:
     sys.path.insert(0, tests)
     from .config.base import read_config_json
     from .config.registry import architecture_name
-    if architecture_name(read_config_json(args.model)) == "Turudra":
-        # the plain implementation of this architecture takes the configuration and the tensors as they are stored
+    arch_name = architecture_name(read_config_json(args.model))
+    if arch_name in ("Turudra", "Besolix"):
+        # the plain implementations of these architectures take the configuration and the tensors as they are stored
+        import importlib
         import numpy as np
-        import plain_turudra
+        plain_turudra = importlib.import_module("plain_" + arch_name.lower())
         from .weights.safetensors_io import open_model_files
         tensors = {n: f.get(n).clone() for f in open_model_files(args.model) for n in f.names()}
         config = read_config_json(args.model)
