@@ -358,10 +358,10 @@ XR_EXPORT int xr_rmsnorm_act(const void* in, int dtype, long long ld_in, const f
 // in: [n, ld_in] rows as one projection wrote them: Q heads [H][D], then K heads [K][D], then V heads [K][Vd].
 // Every Q and K head is divided by its root mean square (eps inside the root) and multiplied by a weight of D values
 // that all heads share (q_w, k_w; null: no norm), in float32; then the first rotary_dim elements are rotated, pair
-// (2j, 2j + 1) or (j, j + rotary_dim/2), by angle = position * freq[j] (a float64 product, cosine and sine rounded to
-// float32).  The attention kernels take one head size hd >= max(D, Vd) for keys and values: Q goes to
-// q_out [n, q_ld] (head h at h * hd), K and V to the token's cache rows, each head filled up to hd with zeros, which
-// change neither a score nor a sum.  One block per token, a warp per head.
+// (2j, 2j + 1) or (j, j + rotary_dim/2), by angle = position * freq[j] (a float64 product brought into [-pi, pi] in
+// float64, cosine and sine in float32).  The attention kernels take one head size hd >= max(D, Vd) for keys and
+// values: Q goes to q_out [n, q_ld] (head h at h * hd), K and V to the token's cache rows, each head filled up to hd
+// with zeros, which change neither a score nor a sum.  One block per token, a warp per head.
 // ---------------------------------------------------------------------------
 struct QkNormStoreArgs {
     const void* in;
@@ -378,6 +378,7 @@ struct QkNormStoreArgs {
     long long page_stride, v_offset;
     int H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent;
     float eps;
+    int pairs;                   // every size, stride and base address is even in elements (set by the launcher)
 };
 
 template <typename T>
@@ -391,9 +392,7 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
     float* cs = qk_sm;
     float* mine = qk_sm + 2 * half + (size_t)warp * a.D;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        double s, c;
-        sincos((double)pos * a.freq[j], &s, &c);
-        cs[j] = (float)c; cs[half + j] = (float)s;
+        xr_sincos_angle((double)pos * a.freq[j], &cs[half + j], &cs[j]);
     }
     T* kdst = nullptr;
     if (a.cache_k != nullptr) {
@@ -405,34 +404,59 @@ k_qk_norm_rope_store(QkNormStoreArgs a) {
     xr_pdl_wait();
     const T* row = (const T*)a.in + (size_t)t * a.ld_in;
     const int heads = kdst ? a.H + a.K : a.H;
+    // bfloat16 rows whose sizes and strides are even: elements are read and written two at a time
+    const bool pairs = sizeof(T) == 2 && a.pairs;
     for (int head = warp; head < heads; head += nw) {
         const T* src = row + (size_t)head * a.D;
         const float* w = head < a.H ? a.q_w : a.k_w;
         float ss = 0.f;
-        for (int e = lane; e < a.D; e += 32) { const float x = xr_to_f32<T>(src[e]); mine[e] = x; ss = fmaf(x, x, ss); }
+        if (pairs) {
+            for (int e = 2 * lane; e < a.D; e += 64) {
+                const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(src) + e));
+                mine[e] = x.x; mine[e + 1] = x.y;
+                ss = fmaf(x.x, x.x, fmaf(x.y, x.y, ss));
+            }
+        } else {
+            for (int e = lane; e < a.D; e += 32) { const float x = xr_to_f32<T>(src[e]); mine[e] = x; ss = fmaf(x, x, ss); }
+        }
         ss = xr_warp_sum(ss);
         const float inv = w != nullptr ? 1.0f / sqrtf(ss / (float)a.D + a.eps) : 1.0f;
         __syncwarp();
         T* dst = head < a.H ? (T*)a.q_out + (size_t)t * a.q_ld + (size_t)head * a.hd : kdst + (size_t)(head - a.H) * head_step;
-        for (int e = lane; e < a.hd; e += 32) {
-            float y = 0.f;
-            if (e < a.D) {
-                y = w != nullptr ? mine[e] * inv * w[e] : mine[e];
-                if (e < a.rotary_dim) {
-                    int j, other; bool first;
-                    if (a.adjacent) { j = e >> 1; first = !(e & 1); other = e ^ 1; }
-                    else { first = e < half; j = first ? e : e - half; other = first ? e + half : e - half; }
-                    const float z = w != nullptr ? mine[other] * inv * w[other] : mine[other];
-                    y = first ? y * cs[j] - z * cs[half + j] : y * cs[j] + z * cs[half + j];
-                }
+        auto value = [&](int e) -> float {
+            if (e >= a.D) return 0.f;
+            float y = w != nullptr ? mine[e] * inv * w[e] : mine[e];
+            if (e < a.rotary_dim) {
+                int j, other; bool first;
+                if (a.adjacent) { j = e >> 1; first = !(e & 1); other = e ^ 1; }
+                else { first = e < half; j = first ? e : e - half; other = first ? e + half : e - half; }
+                const float z = w != nullptr ? mine[other] * inv * w[other] : mine[other];
+                y = first ? y * cs[j] - z * cs[half + j] : y * cs[j] + z * cs[half + j];
             }
-            dst[e] = xr_from_f32<T>(y);
+            return y;
+        };
+        if (pairs) {
+            // two elements a lane, one 4-byte store
+            for (int e = 2 * lane; e < a.hd; e += 64)
+                *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(dst) + e) = __floats2bfloat162_rn(value(e), value(e + 1));
+        } else {
+            for (int e = lane; e < a.hd; e += 32) dst[e] = xr_from_f32<T>(value(e));
         }
         __syncwarp();
     }
     if (kdst == nullptr) return;
     T* vdst = kdst + a.v_offset;
     const T* vsrc = row + (size_t)(a.H + a.K) * a.D;
+    if (pairs && !(a.Vd & 1) && !(a.v_offset & 1) && !(((a.H + a.K) * a.D) & 1)) {
+        const int hd2 = a.hd >> 1;
+        for (int i = threadIdx.x; i < a.K * hd2; i += blockDim.x) {
+            const int kvh = i / hd2, e = (i % hd2) * 2;
+            uint32_t two = 0;                    // (two zeros)
+            if (e < a.Vd) two = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const __nv_bfloat16*>(vsrc) + (size_t)kvh * a.Vd + e);
+            *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(vdst) + (size_t)kvh * head_step + e) = two;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < a.K * a.hd; i += blockDim.x) {
         const int kvh = i / a.hd, e = i % a.hd;
         vdst[(size_t)kvh * head_step + e] = e < a.Vd ? vsrc[(size_t)kvh * a.Vd + e] : xr_from_f32<T>(0.f);
@@ -446,8 +470,9 @@ XR_EXPORT int xr_qk_norm_rope_store(const void* in, int dtype, long long ld_in, 
     if (n < 1 || H < 1 || K < 1 || D < 1 || Vd < 1 || hd < D || hd < Vd || rotary_dim < 0 || rotary_dim > D || (rotary_dim & 1) ||
         page_size < 1 || (rotary_dim > 0 && freq == nullptr) || (q_w == nullptr) != (k_w == nullptr))
         return XR_ERR_ARG;
+    const int pairs = !((D | hd | ld_in | q_ld | page_stride) & 1) && !(((uintptr_t)in | (uintptr_t)q_out | (uintptr_t)cache_k) & 3);
     QkNormStoreArgs a{in, ld_in, q_out, q_ld, positions, tok_seg, block_tables, freq, q_w, k_w, cache_k, page_stride, v_offset,
-                      H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent_pairs ? 1 : 0, eps};
+                      H, K, D, Vd, hd, rotary_dim, max_pages, page_size, adjacent_pairs ? 1 : 0, eps, pairs};
     const size_t smem = ((size_t)rotary_dim + 8 * (size_t)D) * sizeof(float);
     if (smem > 48 * 1024) return XR_ERR_ARG;
     if (dtype == XR_F32) xr_launch((k_qk_norm_rope_store<float>), dim3(n), dim3(256), smem, stream, a);

@@ -17,7 +17,7 @@
 // Preparation, one block per token.  q row t (activation dtype, ldq elements a row): the heads' queries [H][D + R];
 // down row t (ldd elements a row; null with a null cache): the down projection [C + R].
 //  * the last R values of every head's query are rotated in place: the first `rot_dims` of them, pair (i, i + rot_dims/2)
-//    or, with `adjacent`, pair (2i, 2i + 1); angle = position * freq[i], cosine and sine from a float64 angle;
+//    or, with `adjacent`, pair (2i, 2i + 1); angle = position * freq[i] as a float64 product, reduced to [-pi, pi] in float64, cosine and sine in float32;
 //  * c = down[:C] / sqrt(mean(down[:C]^2) + eps) * norm_w and r = rotate(down[C:]) go to the token's cache row.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
@@ -32,9 +32,7 @@ k_latent_prep(T* __restrict__ q, long long ldq, const T* __restrict__ down_all, 
     const int t = blockIdx.x, half = rot_dims / 2;
     const int pos = positions[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        double s, c;
-        sincos((double)pos * freq[i], &s, &c);
-        cs[i] = (float)c; cs[half + i] = (float)s;
+        xr_sincos_angle((double)pos * freq[i], &cs[half + i], &cs[i]);
     }
     xr_pdl_wait();
     __syncthreads();

@@ -857,7 +857,7 @@ def delta(proj: torch.Tensor, conv_w: torch.Tensor, gates: torch.Tensor, neg_a: 
                           dt_bias.data_ptr(), state.data_ptr(), state.stride(0), qkv.data_ptr(), coef.data_ptr(), o.data_ptr(),
                           tok_seg.data_ptr(), seg_start.data_ptr(), seg_len.data_ptr(), seg_slot.data_ptr(), n, n_seg, H, G, D, V, taps,
                           _stream()), "delta")
-    _count(3 if taps > 1 else 2)
+    _count(2)
 
 
 # ---------------------------------------------------------------------------

@@ -1,5 +1,5 @@
-"""Prefill and decode throughput of a Turudra model beside a dense Llama of equal size, with the time of every kernel
-family inside the steps (``bench.py --designs``).
+"""Prefill and decode throughput of a Turudra or a Besolix model beside a dense Llama of equal size, with the time of every
+kernel family inside the steps (``bench.py --designs``).
 
 Sizes resemble real layers; weights are random.  Both models run through the same engine: one prompt of `tokens` tokens
 in one step (prefill), and decode steps of `batch` requests that hold `context` tokens each (``Engine.adopt``: the cache
@@ -19,6 +19,7 @@ from typing import Dict, List
 import torch
 
 from . import kernels, measure
+from .config.besolix import BesolixConfig
 from .config.llama import LlamaConfig
 from .config.turudra import TurudraConfig
 from .engine.engine import EngineParams, StepEntry, random_engine
@@ -50,6 +51,42 @@ def llama_config(size: str, layers: int, positions: int) -> LlamaConfig:
                                   "max_position_embeddings": positions, "torch_dtype": "bfloat16"})
 
 
+BESOLIX_SIZES = {
+    # name: (width, attention, delta, latent, feed-forward, vocab); six layers: delta, latent, attention, delta, a latent layer
+    # that reads the rows of the first, attention
+    "besolix-w1024": (1024, dict(heads=8, kv_heads=2, dim=64, vdim=128, window=1024, rot_dims=32),
+                      dict(heads=4, kv_heads=2, dim=128, vdim=128, conv=4),
+                      dict(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, q_rank=384, window=1024), 2816, 32000),
+    "besolix-w2048": (2048, dict(heads=16, kv_heads=4, dim=128, vdim=128, window=1024, rot_dims=64),
+                      dict(heads=8, kv_heads=4, dim=128, vdim=256, conv=4),
+                      dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, window=1024), 5632, 32000),
+}
+
+
+def besolix_config(size: str) -> BesolixConfig:
+    W, at, dl, la, ff, vocab = BESOLIX_SIZES[size]
+    mlp = {"kind": "dense", "ff": ff}
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": at["heads"], "kv_heads": at["kv_heads"], "dim": at["dim"], "vdim": at["vdim"], "scale": at["dim"] ** -0.5,
+                           "rot": {"base": 20000.0, "dims": at["rot_dims"], "scaling": {"factor": 4.0}}, "mask": {"size": at["window"]}}}
+    delta = {"type": "delta", "mlp": mlp, "mixer": dict(dl)}
+    lm = {k: v for k, v in la.items() if k != "window"}
+    lm.update(scale=(la["dim"] + la["rot_dim"]) ** -0.5, rot={"base": 10000.0, "dims": la["rot_dim"]}, mask={"size": la["window"]})
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": lm}
+    reader = {"type": "latent_attention", "mlp": mlp, "mixer": dict(lm, kv_from=1)}
+    return BesolixConfig.from_dict({"architecture": "Besolix", "vocab": vocab, "width": W, "norm": {"eps": 1e-5},
+                                    "layers": [delta, latent, attention, delta, reader, attention]})
+
+
+def llama_like_besolix(size: str, positions: int) -> LlamaConfig:
+    """A dense decoder of the same width, number of layers, feed-forward and attention window."""
+    W, at, dl, la, ff, vocab = BESOLIX_SIZES[size]
+    return LlamaConfig.from_dict({"architectures": ["LlamaForCausalLM"], "hidden_size": W, "num_hidden_layers": 6,
+                                  "num_attention_heads": W // 128, "num_key_value_heads": max(1, W // 512), "head_dim": 128,
+                                  "intermediate_size": ff, "vocab_size": vocab, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+                                  "max_position_embeddings": positions, "sliding_window": at["window"], "torch_dtype": "bfloat16"})
+
+
 FAMILIES = {
     "gemm_tc": "products (tcgen05)", "gemm_tc_deferred": "products (tcgen05)", "gemm_simt": "products (FMA)",
     "finish_plain": "products (tcgen05)", "finish_add_rmsnorm": "norms", "rmsnorm": "norms", "finish_rope_store": "rotation + cache store",
@@ -59,6 +96,8 @@ FAMILIES = {
     "moe_gather": "grouped products (experts, per-head)", "heads_gather": "grouped products (experts, per-head)",
     "heads_scatter_gate": "grouped products (experts, per-head)",
     "mlstm": "mlstm recurrence", "route_topk": "routing", "moe_plan": "routing", "moe_gemm": "experts' products", "moe_combine": "experts' sum",
+    "delta": "delta recurrence", "head_norm_gate": "delta recurrence", "qk_norm_rope_store": "rotation + cache store",
+    "rmsnorm_act": "norms",
     "scaled_add": "stream kernels", "concat_cast": "stream kernels", "softcap": "stream kernels", "embed": "stream kernels", "act_mul": "stream kernels",
 }
 
@@ -128,10 +167,34 @@ def _work(cfg, tokens: int, keys_per_token: float, decode: bool) -> Dict[str, tu
     return out
 
 
+def _besolix_work(cfg, tokens: int, keys_per_token: float, decode: bool) -> Dict[str, tuple]:
+    """(FLOPs, bytes) that the mixers' own kernel families must move in one step of `tokens` tokens."""
+    fl_a = by_a = fl_l = by_l = fl_h = fl_d = by_d = 0.0
+    for lay in cfg.layers:
+        m = lay.mixer
+        keys = min(keys_per_token, getattr(m, "window", None) or keys_per_token)
+        span = keys if decode else min(2 * keys_per_token, keys_per_token + (getattr(m, "window", None) or keys_per_token))
+        if m.kind == "attention":
+            fl_a += 2.0 * tokens * m.heads * keys * (m.dim + m.vdim)
+            by_a += (tokens if decode else 1) * span * m.kv_heads * 2 * max(m.dim, m.vdim) * 2
+        elif m.kind == "latent_attention":
+            fl_l += 2.0 * tokens * m.heads * keys * (2 * m.kv_rank + m.rot_dim)
+            by_l += (tokens if decode else 1) * span * (m.kv_rank + m.rot_dim) * 2
+            fl_h += 2.0 * tokens * m.heads * m.kv_rank * (m.dim + m.vdim)
+        else:
+            # per token and state element: the decay, S^T k, the update, S^T q
+            fl_d += 7.0 * tokens * m.heads * m.dim * m.vdim
+            by_d += (tokens if decode else 1) * 2 * m.heads * m.dim * m.vdim * 4 + tokens * (2 * m.kv_heads * m.dim + 2 * m.heads * m.vdim) * 4
+    return {"attention": (fl_a, by_a), "latent attention: scores and sums": (fl_l, by_l), "latent attention: per-head products": (fl_h, 0.0),
+            "grouped products (experts, per-head)": (fl_h, 0.0), "delta recurrence": (fl_d, by_d)}
+
+
 def _llama_work(cfg, tokens, keys_per_token, decode):
     L, W = cfg.num_hidden_layers, cfg.hidden_size
-    fl_a = 4.0 * tokens * cfg.num_attention_heads * keys_per_token * cfg.head_dim * L
-    by_a = (tokens if decode else 1) * keys_per_token * 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * L
+    keys = min(keys_per_token, cfg.sliding_window or keys_per_token)
+    span = keys if decode else min(2 * keys_per_token, keys_per_token + (cfg.sliding_window or keys_per_token))
+    fl_a = 4.0 * tokens * cfg.num_attention_heads * keys * cfg.head_dim * L
+    by_a = (tokens if decode else 1) * span * 2 * cfg.num_key_value_heads * cfg.head_dim * 2 * L
     per_layer = W * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * W + 3 * W * cfg.intermediate_size
     fl_p = 2.0 * tokens * (per_layer * L + cfg.vocab_size * W * (1 if decode else 1.0 / tokens))
     by_p = 2.0 * (per_layer * L + cfg.vocab_size * W)
@@ -221,12 +284,16 @@ def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, 
             models=("turudra", "llama"), phase: str = "both") -> dict:
     pk = measure.peaks(root)
     out = {"size": size, "peaks": pk["source"], "dtype": "bf16", "data": "synthetic: random weights, random tokens"}
-    tcfg = turudra_config(size)
     pool = batch * (context + 64 * (2 + (steps + warmup + 8) // 64)) + tokens + 64
     ep = lambda: EngineParams(dtype="bfloat16", max_tokens=pool, page_size=64, max_requests=batch + 1,
                               max_request_tokens=max(tokens, context + steps + warmup + 72), max_step_tokens=tokens)
-    for name, cfg, work in (("turudra", tcfg, _work), ("llama", llama_config(size, len(tcfg.layer_runs()), context + tokens), _llama_work)):
-        if name not in models:
+    if size in BESOLIX_SIZES:
+        arms = (("besolix", besolix_config(size), _besolix_work), ("llama", llama_like_besolix(size, context + tokens), _llama_work))
+    else:
+        tcfg = turudra_config(size)
+        arms = (("turudra", tcfg, _work), ("llama", llama_config(size, len(tcfg.layer_runs()), context + tokens), _llama_work))
+    for name, cfg, work in arms:
+        if name not in models and not (name == "besolix" and "turudra" in models):
             continue
         t0 = time.perf_counter()
         eng = random_engine(cfg, 5, ep())
