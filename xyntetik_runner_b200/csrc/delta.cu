@@ -29,8 +29,12 @@ __global__ void __launch_bounds__(128)
 k_delta_prep(const T* __restrict__ proj, long long ldp, const float* __restrict__ conv_w, const float* __restrict__ gates,
              const float* __restrict__ neg_a, const float* __restrict__ dt_bias, const float* __restrict__ state,
              long long state_stride, long long tail_off, const int* __restrict__ tok_seg, const int* __restrict__ seg_start,
-             const int* __restrict__ seg_slot, float* __restrict__ qkv, float* __restrict__ coef, int H, int G, int D, int V, int taps) {
-    xr_pdl_launch();
+             const int* __restrict__ seg_slot, float* __restrict__ qkv, float* __restrict__ coef, int H, int G, int D, int V, int taps,
+             int early) {
+    // The walk that follows is a few long-lived blocks.  Let in while this kernel's many blocks still hold the machine, they
+    // settle several to an SM wherever room appears first, and the walk, a chain of dependent operations, then takes twice as
+    // long (measured); so only a step of few tokens releases it early.
+    if (early) xr_pdl_launch();
     __shared__ float scratch[33];
     const int t = blockIdx.x, y = blockIdx.y, CH = 2 * G * D + H * V;
     const bool unit = y < 2 * G;
@@ -113,7 +117,6 @@ __global__ void __launch_bounds__(32 * DL_WARPS)
 k_delta_scan(const float* __restrict__ qkv, const float* __restrict__ coef, float* __restrict__ state, long long state_stride,
              float* __restrict__ out, const int* __restrict__ seg_start, const int* __restrict__ seg_len,
              const int* __restrict__ seg_slot, int H, int G, int D, int V, const T* __restrict__ proj, long long ldp, int taps) {
-    xr_pdl_launch();
     constexpr int DP = LPC * RPT, R4 = RPT / 4, DL_COLS = DL_WARPS * 32 / LPC;
     __shared__ __align__(16) float ks[DL_CHUNK][DP];
     __shared__ __align__(16) float qs[DL_CHUNK][DP];
@@ -234,6 +237,7 @@ k_delta_scan(const float* __restrict__ qkv, const float* __restrict__ coef, floa
             }
         }
     }
+    xr_pdl_launch();
     if (taps > 1)
         dl_tail_update<T>(proj, ldp, state + (size_t)slot * state_stride + (size_t)H * V * D, start, len, CH, taps,
                           blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y);
@@ -264,7 +268,8 @@ XR_EXPORT int xr_delta(const void* proj, int dtype, long long ldp, const float* 
 #define DL(T)                                                                                                                        \
     do {                                                                                                                             \
         xr_launch((k_delta_prep<T>), dim3(n, 2 * G + H), dim3(128), 0, stream, (const T*)proj, ldp, conv_w, gates, neg_a, dt_bias,   \
-                  (const float*)state, state_stride, tail_off, tok_seg, seg_start, seg_slot, qkv, coef, H, G, D, V, taps);           \
+                  (const float*)state, state_stride, tail_off, tok_seg, seg_start, seg_slot, qkv, coef, H, G, D, V, taps,            \
+                  n <= 64 ? 1 : 0);                                                                                                  \
         if (D <= 32) DL_SCAN(T, 4, 8);                                                                                               \
         else if (D <= 64) DL_SCAN(T, 8, 8);                                                                                          \
         else if (D <= 128) DL_SCAN(T, 16, 8);                                                                                        \
