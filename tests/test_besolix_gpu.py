@@ -528,13 +528,44 @@ def _drawn_config(rng):
     return tb.model(pick(50, 97, 128), width, pick(1e-5, 1e-6), layers)
 
 
-@pytest.mark.parametrize("seed", range(12))
+def _drawn_config_of_layer_sizes(rng):
+    """The same with sizes like real layers': multiples of 16, several heads, latents of 64 to 256, windows of 40 to 200."""
+    pick = lambda *xs: xs[rng.randint(len(xs))]
+    layers, owners = [], []
+    for i in range(rng.randint(3, 6)):
+        kind = pick("attention", "delta", "latent", "latent")
+        ff = pick(None, 128, 256)
+        if kind == "attention":
+            kv = pick(1, 2, 4)
+            D = pick(32, 64, 96, 128)
+            layers.append(tb.layer(tb.attention(kv * pick(1, 2, 3), kv, D, pick(32, 64, 96, 128), D ** -0.5,
+                                                tb._rot(pick(1e4, 2e4, 5e5), pick(8, 16, 32, D), pick(None, 2.0, 4.0)), pick(None, 48, 64, 96, 200)), ff))
+        elif kind == "delta":
+            G = pick(1, 2, 4)
+            layers.append(tb.layer(tb.delta(G * pick(1, 2), G, pick(32, 64, 128), pick(32, 64, 128), pick(2, 3, 4)), ff))
+        else:
+            reuse = owners and rng.rand() < 0.5
+            if reuse:
+                o = owners[rng.randint(len(owners))]
+                mo = layers[o]["mixer"]
+                C, R, base = mo["kv_rank"], mo["rot_dim"], mo["rot"]["base"]
+            else:
+                C, R, base = pick(64, 96, 128, 192, 256), pick(8, 16, 32), pick(1e4, 5e4)
+            D = pick(16, 32, 64)
+            layers.append(tb.layer(tb.latent(pick(2, 4, 6, 8, 12), D, R, pick(16, 32, 64), C, pick(64, 96, 128), (D + R) ** -0.5,
+                                             base=base, window=pick(None, 40, 72, 100, 128), kv_from=o if reuse else None), ff))
+            if not reuse:
+                owners.append(i)
+    return tb.model(pick(320, 512), pick(128, 192, 256), pick(1e-5, 1e-6), layers)
+
+
+@pytest.mark.parametrize("seed", range(16))
 def test_drawn_configurations(seed):
     rng = np.random.RandomState(1000 + seed)
-    cfg = _drawn_config(rng)
+    cfg = _drawn_config(rng) if seed < 12 else _drawn_config_of_layer_sizes(rng)
     t = tb.draw(cfg, 50 + seed)
-    page = int(rng.choice([4, 8, 16, 64]))
-    reqs = {f"r{i}": traces.random_tokens(7 * seed + i, n, cfg["vocab"]) for i, n in enumerate((3, 90, 17, 140, 1, 45))}
+    page = int(rng.choice([4, 8, 16, 64])) if seed < 12 else 64
+    reqs = {f"r{i}": traces.random_tokens(7 * seed + i, n, cfg["vocab"]) for i, n in enumerate((3, 90, 17, 140, 1, 45) if seed < 12 else (3, 90, 17, 240, 1, 45))}
     ref = {rid: tb.plain_logits(cfg, t, toks) for rid, toks in reqs.items()}
     with tempfile.TemporaryDirectory() as tmp:
         path, _, _ = tb.make_folder(tmp, None, t, cfg)

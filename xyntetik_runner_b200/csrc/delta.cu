@@ -42,7 +42,7 @@ k_delta_prep(const T* __restrict__ proj, long long ldp, const float* __restrict_
     const int seg = tok_seg[t], i = t - seg_start[seg];
     const float* tail = state + (size_t)seg_slot[seg] * state_stride + tail_off;
     xr_pdl_wait();
-    constexpr int OWN = 4;                        // channels per thread: D, V <= 4 * 128 (longer heads take more rounds)
+    constexpr int OWN = 4;                        // channels per thread: D, V <= 4 * 128 (longer heads take more passes)
     float* row = qkv + (size_t)t * CH;
     for (int r0 = 0; r0 < cn; r0 += OWN * 128) {
         float yv[OWN];
@@ -65,7 +65,7 @@ k_delta_prep(const T* __restrict__ proj, long long ldp, const float* __restrict_
             }
         }
         float inv = 1.0f;
-        if (unit) {                               // (a head of more than 512 elements would need its sum over all rounds: refused by the launcher)
+        if (unit) {                               // (a head of more than 512 elements would need its sum over all passes: refused by the launcher)
             ss = xr_block_sum(ss, scratch);
             inv = 1.0f / sqrtf(ss + 1e-6f);
             if (y < G) inv *= 1.0f / sqrtf((float)D);
@@ -88,7 +88,7 @@ k_delta_prep(const T* __restrict__ proj, long long ldp, const float* __restrict_
 // tail[j] <- the input at place len - (taps - 1) + j of the portion: a row of this step, or, where the portion is
 // shorter than the tail, what the tail held len places further on.  All blocks of the scan that walk a portion share
 // its channels (block `part` of `parts`), after the kernel that read the old tail is complete; a thread reads all of a
-// channel's values before it writes any (eight at a time: the reads of a round lie ahead of its writes, j ascends).
+// channel's values before it writes any (eight at a time: the reads of a pass lie ahead of its writes, j ascends).
 template <typename T>
 __device__ __forceinline__ void dl_tail_update(const T* __restrict__ proj, long long ldp, float* tail, int start, int len,
                                                int CH, int taps, int part, int parts) {
