@@ -264,9 +264,10 @@ k_mlstm_scan(const T* __restrict__ proj, long long ldp, int q_col, int k_col, in
 // o [n][H][V] float32 -> y [n][H * V] (activation dtype): o / rms(o over the head) * w * act(g); one warp per (token, head).
 // The weight of head h starts at w + h * w_head (0: one weight of V values for all heads); act is the sigmoid, or SiLU
 // with `gate_silu`.
-template <typename T>
+// (TG: the gate's dtype, the activation dtype or float32)
+template <typename T, typename TG = T>
 __global__ void __launch_bounds__(128)
-k_mlstm_out(const float* __restrict__ o, const T* __restrict__ proj, long long ldp, int g_col, const float* __restrict__ w,
+k_mlstm_out(const float* __restrict__ o, const TG* __restrict__ proj, long long ldp, int g_col, const float* __restrict__ w,
             T* __restrict__ y, int n, int H, int V, float eps, int w_head, int gate_silu) {
     xr_pdl_launch();
     xr_pdl_wait();
@@ -279,10 +280,10 @@ k_mlstm_out(const float* __restrict__ o, const T* __restrict__ proj, long long l
     for (int i = lane; i < V; i += 32) ss = fmaf(src[i], src[i], ss);
     ss = xr_warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)V + eps);
-    const T* g = proj + (size_t)t * ldp + g_col + (size_t)h * V;
+    const TG* g = proj + (size_t)t * ldp + g_col + (size_t)h * V;
     T* dst = y + (size_t)t * H * V + (size_t)h * V;
     for (int i = lane; i < V; i += 32) {
-        const float z = xr_to_f32<T>(g[i]);
+        const float z = xr_to_f32<TG>(g[i]);
         float gate = 1.0f / (1.0f + expf(-z));
         if (gate_silu) gate *= z;
         dst[i] = xr_from_f32<T>(src[i] * inv * w[(size_t)h * w_head + i] * gate);
@@ -337,18 +338,21 @@ XR_EXPORT int xr_mlstm(const void* proj, int dtype, long long ldp, int q_col, in
     return xr_launch_status();
 }
 
-// The last step alone, for other recurrences: y [n][H * V] = o / rms(o per head) * w * act(gate), gate [n][ld_gate] (activation
-// dtype) from column 0, head h at h * V; w_head: elements between the heads' weights (0: one weight for all heads).
-XR_EXPORT int xr_head_norm_gate(const float* o, const void* gate, int dtype, long long ld_gate, const float* w, int w_head, int gate_silu,
-                                void* y, int n, int H, int V, float eps, cudaStream_t stream) {
+// The last step alone, for other recurrences: y [n][H * V] (dtype `dtype`) = o / rms(o per head) * w * act(gate), gate [n][ld_gate]
+// (dtype `gate_dtype`: that of y, or float32) from column 0, head h at h * V; w_head: elements between the heads' weights (0: one
+// weight for all heads).
+XR_EXPORT int xr_head_norm_gate(const float* o, const void* gate, int gate_dtype, long long ld_gate, const float* w, int w_head, int gate_silu,
+                                void* y, int dtype, int n, int H, int V, float eps, cudaStream_t stream) {
     if (n < 1 || H < 1 || V < 1 || w_head < 0) return XR_ERR_ARG;
     const long long warps = (long long)n * H;
     const unsigned gb = (unsigned)((warps + 3) / 4);
-    if (dtype == XR_F32)
-        xr_launch((k_mlstm_out<float>), dim3(gb), dim3(128), 0, stream, o, (const float*)gate, ld_gate, 0, w, (float*)y, n, H, V, eps, w_head, gate_silu);
-    else if (dtype == XR_BF16)
-        xr_launch((k_mlstm_out<__nv_bfloat16>), dim3(gb), dim3(128), 0, stream, o, (const __nv_bfloat16*)gate, ld_gate, 0, w,
-                  (__nv_bfloat16*)y, n, H, V, eps, w_head, gate_silu);
+    typedef __nv_bfloat16 bf;
+    if (dtype == XR_F32 && gate_dtype == XR_F32)
+        xr_launch((k_mlstm_out<float, float>), dim3(gb), dim3(128), 0, stream, o, (const float*)gate, ld_gate, 0, w, (float*)y, n, H, V, eps, w_head, gate_silu);
+    else if (dtype == XR_BF16 && gate_dtype == XR_BF16)
+        xr_launch((k_mlstm_out<bf, bf>), dim3(gb), dim3(128), 0, stream, o, (const bf*)gate, ld_gate, 0, w, (bf*)y, n, H, V, eps, w_head, gate_silu);
+    else if (dtype == XR_BF16 && gate_dtype == XR_F32)
+        xr_launch((k_mlstm_out<bf, float>), dim3(gb), dim3(128), 0, stream, o, (const float*)gate, ld_gate, 0, w, (bf*)y, n, H, V, eps, w_head, gate_silu);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }

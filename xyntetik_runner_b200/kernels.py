@@ -82,7 +82,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_qk_norm_rope_store": [_vp, _i, _ll, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_rmsnorm_act": [_vp, _i, _ll, _vp, _vp, _ll, _i, _i, _f, _vp],
         "xr_delta": [_vp, _i, _ll, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-        "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _f, _vp],
+        "xr_head_norm_gate": [_vp, _vp, _i, _ll, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _vp],
         "xr_mlstm": [_vp, _i, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
         "xr_route_topk": [_vp, _vp, _vp, _i, _i, _i, _vp],
         "xr_moe_plan": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -818,15 +818,16 @@ def mlstm(proj: torch.Tensor, cols, gates: torch.Tensor, state: torch.Tensor, co
 
 def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_col: int, w: torch.Tensor, y: torch.Tensor, H: int, V: int, eps: float,
                    per_head_weight: bool = False, silu: bool = False) -> None:
-    """y [n, H V] = o / rms(o per head) * w * act(gate[:, gate_col + h V + i]): o float32 [n, H V]; gate and y in the activation
-    dtype; w float32, V values for all heads or (`per_head_weight`) H V; act the sigmoid, or SiLU with `silu`."""
+    """y [n, H V] = o / rms(o per head) * w * act(gate[:, gate_col + h V + i]): o float32 [n, H V]; y in the activation dtype, gate
+    in y's dtype or float32; w float32, V values for all heads or (`per_head_weight`) H V; act the sigmoid, or SiLU with `silu`."""
     _dev(o, w, y)
     n = o.shape[0]
-    assert o.dtype == torch.float32 and o.shape == (n, H * V) and y.shape == (n, H * V) and gate.dtype == y.dtype and gate.stride(1) == 1
+    assert o.dtype == torch.float32 and o.shape == (n, H * V) and y.shape == (n, H * V) and gate.stride(1) == 1
+    assert gate.dtype in (y.dtype, torch.float32)
     assert w.dtype == torch.float32 and w.numel() == (H * V if per_head_weight else V) and gate.shape[1] >= gate_col + H * V
     _check(lib().xr_head_norm_gate(o.data_ptr(), gate.data_ptr() + gate_col * gate.element_size(), dtype_code(gate.dtype), gate.stride(0),
-                                   w.data_ptr(), V if per_head_weight else 0, int(silu), y.data_ptr(), n, H, V, float(eps), _stream()),
-           "head_norm_gate")
+                                   w.data_ptr(), V if per_head_weight else 0, int(silu), y.data_ptr(), dtype_code(y.dtype), n, H, V,
+                                   float(eps), _stream()), "head_norm_gate")
     _count()
 
 

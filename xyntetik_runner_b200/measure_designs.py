@@ -293,6 +293,7 @@ def compare(size: str, tokens: int = 2048, batch: int = 8, context: int = 2048, 
         tcfg = turudra_config(size)
         arms = (("turudra", tcfg, _work), ("llama", llama_config(size, len(tcfg.layer_runs()), context + tokens), _llama_work))
     for name, cfg, work in arms:
+        # (`models` names arms to run; "turudra" also stands for the new design's arm of a Besolix size: the default runs both arms)
         if name not in models and not (name == "besolix" and "turudra" in models):
             continue
         t0 = time.perf_counter()

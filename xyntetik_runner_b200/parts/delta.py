@@ -9,7 +9,7 @@ current token's, zeros before a request's first token):
     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q                              S [D, V] per value head
     y = W_o (concat_i(o_i / rms(o_i)) * w * silu(W_g h))                                          w: V values for all heads
 S starts at zero and lives in float32 in the request's state slot together with the last taps - 1 rows that entered the
-convolutions; everything after the projections is float32 in both precisions (csrc/delta.cu).  The state after a token
+convolutions; the projections' sums and everything after them are float32 in both precisions (csrc/delta.cu).  The state after a token
 does not depend on how tokens were cut into steps.
 """
 from __future__ import annotations
@@ -79,7 +79,9 @@ class GatedDelta(Mixer):
         n, H, V, CH = h.shape[0], self.H, self.V, self.channels
         total = CH + H * V
         ld = -(-total // 8) * 8
-        proj = ctx.buf("delta_proj", (n, ld), ctx.act_dtype)[:, :total]
+        # the projections leave their product in float32: what enters the convolutions and the recurrence is rounded once, at the
+        # product's input, and the convolutions' tail holds exactly what the rows held
+        proj = ctx.buf("delta_proj", (n, ld), torch.float32)[:, :total]
         self.proj.forward(h, proj)
         gates = ctx.buf("delta_gates", (n, 2 * H), torch.float32)
         self.gates.forward(h, gates)
