@@ -63,6 +63,13 @@ def test_a_reader_of_a_readers_rows_is_refused():
         BesolixConfig.from_dict(d)
 
 
+def test_a_reader_may_leave_what_it_shares_to_the_owner():
+    d = copy.deepcopy(tb.CONFIGS["mix"])
+    for key in ("kv_rank", "rot_dim", "rot"):
+        d["layers"][3]["mixer"].pop(key)
+    assert BesolixConfig.from_dict(d) == BesolixConfig.from_dict(tb.CONFIGS["mix"])
+
+
 def test_shared_rows_are_kept_for_the_longest_window_among_their_readers():
     plan = registry.resolve("Besolix").build_plan(BesolixConfig.from_dict(tb.CONFIGS["mix"]))
     assert plan.schedule[3].cache_from == 1 and plan.schedule[1].cache_from is None

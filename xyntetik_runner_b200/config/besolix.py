@@ -188,7 +188,16 @@ class BesolixConfig:
                 raise ConfigError(f"config.json: {where}.type '{kind}' is not supported (known: {', '.join(sorted(cls.MIXERS))})")
             if not isinstance(lr.get("mixer"), Mapping):
                 raise ConfigError(f"config.json: {where} lacks 'mixer'")
-            mixer = cls.MIXERS[kind].from_dict(lr["mixer"], where + ".mixer")
+            md = lr["mixer"]
+            j = md.get("kv_from")
+            if kind == "latent_attention" and isinstance(j, int) and not isinstance(j, bool) and 0 <= j < i \
+                    and isinstance(raw[j], Mapping) and isinstance(raw[j].get("mixer"), Mapping):
+                # what a reader of another layer's rows shares with that layer may be left to it
+                md = dict(md)
+                for key in ("kv_rank", "rot_dim", "rot"):
+                    if md.get(key) is None and raw[j]["mixer"].get(key) is not None:
+                        md[key] = raw[j]["mixer"][key]
+            mixer = cls.MIXERS[kind].from_dict(md, where + ".mixer")
             mlp = DenseConfig.from_dict(lr["mlp"], where + ".mlp") if lr.get("mlp") else None
             layers.append(LayerConfig(mixer, mlp))
         for i, lay in enumerate(layers):
